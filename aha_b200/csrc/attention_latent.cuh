@@ -101,10 +101,11 @@ namespace aha {
 //                          4 ty .. 4 ty + 3 against keys tx + 16 i, then the outputs of the same queries in columns tx + 16 j, so the
 //                          running maximum and sum of a query never leave its threads (the 16 threads of a row meet by shuffles)
 // while decoded tokens and short portions stay on the absorbed form above.
-static __global__ void latent_gather_kernel(PagedKV kv, const int* __restrict__ page_table, float* __restrict__ out, int S) {
+// rows of positions s0 .. s0 + S - 1 (s0 > 0: a sliding window needs nothing before its first query's first key)
+static __global__ void latent_gather_kernel(PagedKV kv, const int* __restrict__ page_table, float* __restrict__ out, int s0, int S) {
     const int s = blockIdx.x;
     if (s >= S) return;
-    const float* row = kv.k_row(page_table[s >> kPageShift], 0, s & (kPage - 1));
+    const float* row = kv.k_row(page_table[(s0 + s) >> kPageShift], 0, (s0 + s) & (kPage - 1));
     for (int i = threadIdx.x; i < kv.D; i += blockDim.x) out[(size_t)s * kv.D + i] = row[i];
 }
 
@@ -115,9 +116,11 @@ struct LatentFlashArgs {
     const float* vx; int ld_v; int v_head_stride;          // [S, .] expanded values
     const float* k_rot; int ld_kr;                         // [S, .] rotated key part shared by the heads
     float* out; int ld_o;                                  // [T, H * Dv]
-    int t0, n, pos0;                                       // the entry's packed rows t0 .. t0 + n - 1 are positions pos0 .. pos0 + n - 1
+    int t0, n, pos0;                                       // the entry's packed rows t0 .. t0 + n - 1 are positions pos0 .. pos0 + n - 1 (counted from the
+                                                           // first expanded key, which need not be the sequence's first token)
     int D, R, Dv;
     float scale;
+    int window = 0;                                        // > 0: query i sees keys j with 0 <= i - j < window
 };
 
 constexpr int kLfBQ = 64, kLfBK = 64, kLfThreads = 256;
@@ -184,8 +187,10 @@ static __global__ void __launch_bounds__(kLfThreads) latent_flash_kernel(LatentF
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    load_k(0);
-    load_v(0);
+    // keys before the window of the tile's first query are never visited
+    const int k_begin = a.window > 0 ? max(0, a.pos0 + q0 - a.window + 1) / kLfBK * kLfBK : 0;
+    load_k(k_begin);
+    load_v(k_begin);
     for (int idx = tid; idx < kLfBQ * ldq; idx += kLfThreads) {
         const int r = idx / ldq, d = idx % ldq;
         float v = 0.f;
@@ -203,7 +208,7 @@ static __global__ void __launch_bounds__(kLfThreads) latent_flash_kernel(LatentF
 #pragma unroll
         for (int j = 0; j < NV; ++j) o[i][j] = 0.f;
     }
-    for (int k0 = 0; k0 <= last_pos; k0 += kLfBK) {
+    for (int k0 = k_begin; k0 <= last_pos; k0 += kLfBK) {
         const int nk = min(kLfBK, last_pos + 1 - k0);
         asm volatile("cp.async.wait_group 1;" ::: "memory");      // this tile's keys (its values may still be on their way)
         __syncthreads();
@@ -236,7 +241,7 @@ static __global__ void __launch_bounds__(kLfThreads) latent_flash_kernel(LatentF
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int j = k0 + tx + 16 * u;
-                if (j > qpos || tx + 16 * u >= nk) s[i][u] = -INFINITY;
+                if (j > qpos || tx + 16 * u >= nk || (a.window > 0 && qpos - j >= a.window)) s[i][u] = -INFINITY;
                 mx = fmaxf(mx, s[i][u]);
             }
 #pragma unroll
@@ -335,6 +340,7 @@ struct LatentDecodeArgs {
     float scale;
     float* part; int nsplit, chunk;  // see WindowAttnArgs
     int H;
+    int window;                      // > 0: token i sees keys j with 0 <= i - j < window
     RaggedBatch rb;
 };
 
@@ -350,7 +356,7 @@ static __global__ void __launch_bounds__(kLdThreads) latent_decode_attn_kernel(L
     const int t = blockIdx.x, z = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int e = a.rb.tok_entry[t], i = a.rb.tok_pos[t], slot = a.rb.ent_slot[e];
     const int* pt = a.rb.page_tables + (size_t)slot * a.rb.max_pages;
-    const int ja = z * a.chunk, jb = min(ja + a.chunk, i + 1);
+    const int ja = (a.window > 0 ? max(0, i - a.window + 1) : 0) + z * a.chunk, jb = min(ja + a.chunk, i + 1);
     const bool vec = (Dk & 3) == 0;
     for (int g0 = 0; g0 < a.H; g0 += kLdHG) {
         const int hg = min(kLdHG, a.H - g0);
@@ -463,7 +469,7 @@ inline int latent_decode_attn(cudaStream_t st, WindowAttnArgs w, int kv_span) {
     w.chunk = ceil_div(ceil_div(kv_span, w.nsplit), kPage) * kPage;
     w.skip_from_n = 0;
     LatentDecodeArgs a{};
-    a.q = w.q; a.ld_q = w.H * w.kv.D; a.kv = w.kv; a.scale = w.scale; a.part = w.part; a.nsplit = w.nsplit; a.chunk = w.chunk; a.H = w.H; a.rb = w.rb;
+    a.q = w.q; a.ld_q = w.H * w.kv.D; a.kv = w.kv; a.scale = w.scale; a.part = w.part; a.nsplit = w.nsplit; a.chunk = w.chunk; a.H = w.H; a.window = w.window; a.rb = w.rb;
     static bool attr = false;
     if (!attr) { AHA_CUDA_CHECK(cudaFuncSetAttribute(latent_decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)); attr = true; }
     latent_decode_attn_kernel<<<dim3(w.rb.T, w.nsplit), kLdThreads, latent_decode_smem(w.kv.D), st>>>(a);

@@ -82,7 +82,7 @@ inline size_t latent_flash_tc_ws_halfs(int H, int n, int S, int D, int R, int Dv
     return 2 * ((size_t)H * n * HDQ + (size_t)H * S * HDQ + (size_t)H * Dv * flash_tc_skv_pad(S));
 }
 
-template <int HD, int HDQ>
+template <int HD, int HDQ, bool WIN>
 inline void latent_flash_tc_launch(cudaStream_t st, const LatentFlashArgs& a, int H, int S, __half* ws) {
     const int pad = flash_tc_skv_pad(S);
     LatentSplitArgs sp;
@@ -97,16 +97,24 @@ inline void latent_flash_tc_launch(cudaStream_t st, const LatentFlashArgs& a, in
     const CUtensorMap tvh = make_tmap_f16_box(sp.vt_hi, (uint64_t)H * HD, (uint64_t)pad, HD), tvl = make_tmap_f16_box(sp.vt_lo, (uint64_t)H * HD, (uint64_t)pad, HD);
     FlashTcArgs m;
     m.out = a.out; m.o_tok_stride = (size_t)a.ld_o; m.o_head_stride = (size_t)HD; m.out_hi = nullptr; m.out_lo = nullptr;
-    m.Sq = a.n; m.Skv = S; m.q0 = a.t0; m.groups = 1; m.scaling = a.scale;
-    flash_attn_tc_kernel<HD, true, false, HDQ><<<dim3(ceil_div(a.n, kFaBQ), H), kFaThreads, flash_tc_smem_bytes<HD, HDQ>(), st>>>(tqh, tql, tkh, tkl, tvh, tvl, m);
+    m.Sq = a.n; m.Skv = S; m.q0 = a.t0; m.groups = 1; m.scaling = a.scale; m.window = a.window;
+    static bool attr = false;      // (the instances the library's start-up does not know)
+    if (!attr) { AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<HD, true, WIN, HDQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)flash_tc_smem_bytes<HD, HDQ>())); attr = true; }
+    flash_attn_tc_kernel<HD, true, WIN, HDQ><<<dim3(ceil_div(a.n, kFaBQ), H), kFaThreads, flash_tc_smem_bytes<HD, HDQ>(), st>>>(tqh, tql, tkh, tkl, tvh, tvl, m);
     AHA_CUDA_CHECK(cudaGetLastError());
 }
 
-// a: as for latent_flash (the entry's queries, the expanded keys / values of positions 0 .. S - 1).  Returns the launches.
+// a: as for latent_flash (the entry's queries, the expanded keys / values of positions 0 .. S - 1).  A sliding window runs the kernel's
+// windowed instances.  Returns the launches.
 inline int latent_flash_tc(cudaStream_t st, const LatentFlashArgs& a, int H, __half* ws) {
     const int S = a.pos0 + a.n, HDQ = latent_flash_tc_hdq(a.D, a.R, a.Dv);
-    if (a.Dv == 128) { if (HDQ == 128) latent_flash_tc_launch<128, 128>(st, a, H, S, ws); else latent_flash_tc_launch<128, 192>(st, a, H, S, ws); }
-    else { if (HDQ == 64) latent_flash_tc_launch<64, 64>(st, a, H, S, ws); else latent_flash_tc_launch<64, 128>(st, a, H, S, ws); }
+    if (a.window > 0) {
+        if (a.Dv == 128) { if (HDQ == 128) latent_flash_tc_launch<128, 128, true>(st, a, H, S, ws); else latent_flash_tc_launch<128, 192, true>(st, a, H, S, ws); }
+        else { if (HDQ == 64) latent_flash_tc_launch<64, 64, true>(st, a, H, S, ws); else latent_flash_tc_launch<64, 128, true>(st, a, H, S, ws); }
+        return 2;
+    }
+    if (a.Dv == 128) { if (HDQ == 128) latent_flash_tc_launch<128, 128, false>(st, a, H, S, ws); else latent_flash_tc_launch<128, 192, false>(st, a, H, S, ws); }
+    else { if (HDQ == 64) latent_flash_tc_launch<64, 64, false>(st, a, H, S, ws); else latent_flash_tc_launch<64, 128, false>(st, a, H, S, ws); }
     return 2;
 }
 

@@ -5,11 +5,19 @@
 //                          state), an optional RMS norm of q and of k over the WHOLE projection (all heads at once), then K (convolved,
 //                          normed) and V (convolved) go to the cache at the token's position and q to a dense buffer
 //   conv_tail_update_kernel  leaves the last taps - 1 projected values of every entry in its slot
+//   qk_rotary_norm_kernel  the other prologue: rotary positions on interleaved pairs of the first coordinates of every q and k head (a frequency
+//                          table from the host, angle = position * frequency in fp32), then an optional division of every head by its own
+//                          root mean square (a unit norm, no gain); K and V go to the cache, q to a dense buffer
 //   window_attn_kernel     softmax attention of query head h over kv head h / (H / G) with
 //                              score(i, j) = q_i . k_j * scale - slope_h * (i - j),   visible: 0 <= i - j < window  (window 0: all j <= i)
-//                          and an optional sigmoid output gate.  slope_h comes from a table, so any bias schedule can be passed.
+//                          and an optional sigmoid output gate (a number per channel or one per head).  slope_h comes from a table, so any
+//                          bias schedule can be passed.  `sink`: the softmax denominator holds an extra exp(0) -- a key of score 0 without
+//                          a value, so a head may attend to nothing.
 // Positions, scores, softmax weights and norms are fp32; the cache is fp32.  A token's result depends only on its own sequence.
 #pragma once
+#include <cmath>
+#include <vector>
+
 #include "common.cuh"
 #include "ragged.cuh"
 
@@ -124,6 +132,90 @@ static __global__ void __launch_bounds__(256) conv_tail_update_kernel(QkvPrepArg
     }
 }
 
+struct RotaryPrepArgs {
+    const float* proj; int ld;       // [T, ld] projected rows
+    int q_off, k_off, v_off;
+    int H, G, D, Dv;
+    const float* freq; int n_freq;   // coordinates (2i, 2i + 1), i < n_freq, of every head turn by position * freq[i]; the rest pass
+    int unit_norm; float eps;        // 1: after the rotation every q and k head is divided by sqrt(mean(head^2) + eps)
+    float* q_out;                    // [T, H * D]
+    PagedKV kv;
+    RaggedBatch rb;
+};
+
+// One block per token.  cos / sin of the token's angles are formed once (shared memory); a warp takes a head of q or k at a time, a lane a
+// pair of coordinates.
+static __global__ void __launch_bounds__(256) qk_rotary_norm_kernel(RotaryPrepArgs a) {
+    extern __shared__ float rot_cs[];      // [n_freq] cos, [n_freq] sin
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    const int e = a.rb.tok_entry[t], pos = a.rb.tok_pos[t], slot = a.rb.ent_slot[e];
+    const float fpos = (float)pos;
+    for (int i = tid; i < a.n_freq; i += blockDim.x) {
+        float sn, cs;
+        sincosf(fpos * a.freq[i], &sn, &cs);
+        rot_cs[i] = cs; rot_cs[a.n_freq + i] = sn;
+    }
+    __syncthreads();
+    const int page = a.rb.page_tables[(size_t)slot * a.rb.max_pages + (pos >> kPageShift)], tip = pos & (kPage - 1);
+    const float* row = a.proj + (size_t)t * a.ld;
+    const int pairs = (a.D + 1) / 2;
+    for (int item = warp; item < a.H + a.G; item += nw) {
+        const bool isq = item < a.H;
+        const float* src = isq ? row + a.q_off + (size_t)item * a.D : row + a.k_off + (size_t)(item - a.H) * a.D;
+        float* dst = isq ? a.q_out + (size_t)t * a.H * a.D + (size_t)item * a.D : a.kv.k_row(page, item - a.H, tip);
+        float ss = 0.f;
+        for (int j = lane; j < pairs; j += 32) {
+            const bool two = 2 * j + 1 < a.D;
+            float u = src[2 * j], v = two ? src[2 * j + 1] : 0.f;
+            if (j < a.n_freq) {
+                const float cs = rot_cs[j], sn = rot_cs[a.n_freq + j];
+                const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+                u = ru; v = rv;
+            }
+            dst[2 * j] = u;
+            if (two) dst[2 * j + 1] = v;
+            ss = fmaf(u, u, fmaf(v, v, ss));
+        }
+        if (a.unit_norm) {
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)a.D + a.eps);
+            for (int j = lane; j < pairs; j += 32) {       // a lane rereads what it wrote itself
+                dst[2 * j] *= inv;
+                if (2 * j + 1 < a.D) dst[2 * j + 1] *= inv;
+            }
+        }
+    }
+    for (int c = tid; c < a.G * a.Dv; c += blockDim.x) a.kv.v_row(page, c / a.Dv, tip)[c % a.Dv] = row[a.v_off + c];
+}
+
+inline int qk_rotary_prepare(cudaStream_t st, const RotaryPrepArgs& a) {
+    if (a.rb.T == 0) return 0;
+    AHA_REQUIRE(2 * a.n_freq <= a.D, "rotary: more rotated coordinates than the head has");
+    qk_rotary_norm_kernel<<<a.rb.T, 256, 2 * (size_t)std::max(1, a.n_freq) * sizeof(float), st>>>(a);
+    AHA_CUDA_CHECK(cudaGetLastError());
+    return 1;
+}
+
+// Rotary frequencies f_i = base^(-2i / dims), i < dims / 2, optionally rescaled band by band (host, double): with wavelength 2 pi / f, waves
+// shorter than original / high are kept, waves longer than original / low are divided by `factor`, and between the two the frequency moves
+// linearly in s = (original / wavelength - low) / (high - low) from f / factor (s = 0) to f (s = 1).  factor <= 0: no rescaling.
+inline void banded_rotary_frequencies(int dims, double base, double factor, double low, double high, double original, std::vector<float>& freq) {
+    const double pi = 3.14159265358979323846;
+    freq.resize(dims / 2);
+    for (int i = 0; i < dims / 2; ++i) {
+        double f = std::pow(base, -2.0 * i / dims);
+        if (factor > 0) {
+            const double wl = 2.0 * pi / f;
+            if (wl > original / low) f = f / factor;
+            else if (!(wl < original / high)) {
+                const double s = (original / wl - low) / (high - low);
+                f = (1.0 - s) * f / factor + s * f;
+            }
+        }
+        freq[i] = (float)f;
+    }
+}
+
 struct WindowAttnArgs {
     const float* q;          // [T, H*D]
     PagedKV kv;
@@ -131,6 +223,8 @@ struct WindowAttnArgs {
     float scale;
     int window;              // 0 = every earlier position
     const float* gate; int gate_ld;   // raw gate pre-activations [T, .] (column h*Dv + c) or nullptr
+    int gate_per_head = 0;   // 1: the gate has ONE number per head (column h)
+    int sink = 0;            // 1: one is added to the softmax denominator (a key of score 0 that has no value)
     float* out;              // [T, H*Dv]
     int H;
     RaggedBatch rb;
@@ -231,13 +325,17 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_kernel(Win
         }
         return;
     }
-    const float inv = 1.0f / l;
+    float inv = 1.0f / l;
+    if (a.sink) {                      // bring the sums to max(m, 0), the maximum once the score 0 takes part
+        const float M = fmaxf(m, 0.f), w = expf(m - M);
+        inv = w / (l * w + expf(-M));
+    }
 #pragma unroll
     for (int r = 0; r < kWinAttnMaxAcc; ++r) {
         const int c = tid + r * kWinAttnThreads;
         if (c < Dv) {
             float o = acc[r] * inv;
-            if (a.gate) o *= sigmoid_f(a.gate[(size_t)t * a.gate_ld + h * Dv + c]);
+            if (a.gate) o *= sigmoid_f(a.gate[(size_t)t * a.gate_ld + (a.gate_per_head ? h : h * Dv + c)]);
             a.out[(size_t)t * a.H * Dv + h * Dv + c] = o;
         }
     }
@@ -253,9 +351,10 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_merge_kern
     const float* P = a.part + ((size_t)t * a.H + h) * a.nsplit * (size_t)(2 + Dv);
     const bool mine = tid < a.nsplit;
     const float ms = mine ? P[(size_t)tid * (2 + Dv)] : -INFINITY, ls = mine ? P[(size_t)tid * (2 + Dv) + 1] : 0.f;
-    const float M = block_max(ms, red);
+    float M = block_max(ms, red);
+    if (a.sink) M = fmaxf(M, 0.f);
     const float wgt = ls > 0.f ? expf(ms - M) : 0.f;
-    const float L = block_sum(ls * wgt, red);
+    const float L = block_sum(ls * wgt, red) + (a.sink ? expf(-M) : 0.f);
     if (mine) wsm[tid] = wgt / L;
     __syncthreads();
     float o[kWinAttnMaxAcc];          // channels tid, tid + 128, ...: their loads of a chunk are in flight together
@@ -277,7 +376,7 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_merge_kern
         const int c = tid + r * kWinAttnThreads;
         if (c < Dv) {
             float v = o[r];
-            if (a.gate) v *= sigmoid_f(a.gate[(size_t)t * a.gate_ld + h * Dv + c]);
+            if (a.gate) v *= sigmoid_f(a.gate[(size_t)t * a.gate_ld + (a.gate_per_head ? h : h * Dv + c)]);
             a.out[(size_t)t * a.H * Dv + h * Dv + c] = v;
         }
     }

@@ -97,12 +97,15 @@ __device__ __forceinline__ float xielu_f(float z, float alpha_p, float alpha_n) 
 }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 
-enum Act { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_ERF = 2, ACT_GELU_TANH = 3, ACT_XIELU = 4 /* two parameters: callers use xielu_f */ };
+__device__ __forceinline__ float relu2_f(float x) { const float r = fmaxf(x, 0.f); return r * r; }      // the square of relu
+
+enum Act { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_ERF = 2, ACT_GELU_TANH = 3, ACT_XIELU = 4 /* two parameters: callers use xielu_f */, ACT_RELU2 = 5 };
 __device__ __forceinline__ float apply_act(int act, float x) {
     switch (act) {
         case ACT_SILU: return silu_f(x);
         case ACT_GELU_ERF: return gelu_erf_f(x);
         case ACT_GELU_TANH: return gelu_tanh_f(x);
+        case ACT_RELU2: return relu2_f(x);
         default: return x;
     }
 }

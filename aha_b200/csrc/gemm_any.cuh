@@ -12,7 +12,7 @@
 
 namespace aha {
 
-enum AnyEpi { AEPI_STORE = 0, AEPI_XIELU = 1, AEPI_SWIGLU = 2 };   // SWIGLU: rows of W alternate gate / up; C[m][n / 2] = silu(gate) * up (N even)
+enum AnyEpi { AEPI_STORE = 0, AEPI_XIELU = 1, AEPI_SWIGLU = 2, AEPI_RELU2 = 3 };   // SWIGLU: rows of W alternate gate / up; C[m][n / 2] = silu(gate) * up (N even); RELU2: max(v, 0)^2
 
 struct GemmAnyArgs {
     const float* A; int lda;
@@ -63,6 +63,7 @@ template <int EPI>
 __device__ __forceinline__ float any_epilogue(const GemmAnyArgs& g, float v, int n) {
     if (g.bias) v += g.bias[n];
     if (EPI == AEPI_XIELU) v = xielu_f(v, g.act_a, g.act_b);
+    if (EPI == AEPI_RELU2) v = relu2_f(v);
     return v;
 }
 
@@ -287,16 +288,18 @@ inline void gemm_any_launch(cudaStream_t st, const GemmAnyArgs& g, int num_sms) 
 // fp32_weights: W holds floats, else bf16
 inline void gemm_any(cudaStream_t st, int epi, bool fp32_weights, const GemmAnyArgs& g, int num_sms) {
     if (g.M == 0 || g.N == 0) return;
-    AHA_REQUIRE(epi == AEPI_STORE || epi == AEPI_XIELU || epi == AEPI_SWIGLU, "gemm_any: bad epilogue");
+    AHA_REQUIRE(epi == AEPI_STORE || epi == AEPI_XIELU || epi == AEPI_SWIGLU || epi == AEPI_RELU2, "gemm_any: bad epilogue");
     AHA_REQUIRE(epi != AEPI_SWIGLU || g.N % 2 == 0, "gemm_any: the gate / up epilogue needs an even number of weight rows");
     AHA_REQUIRE(g.batch >= 1 && g.batch <= 65535, "gemm_any: bad batch count");
     if (fp32_weights) {
         if (epi == AEPI_STORE) gemm_any_launch<float, AEPI_STORE>(st, g, num_sms);
         else if (epi == AEPI_XIELU) gemm_any_launch<float, AEPI_XIELU>(st, g, num_sms);
+        else if (epi == AEPI_RELU2) gemm_any_launch<float, AEPI_RELU2>(st, g, num_sms);
         else gemm_any_launch<float, AEPI_SWIGLU>(st, g, num_sms);
     } else {
         if (epi == AEPI_STORE) gemm_any_launch<__nv_bfloat16, AEPI_STORE>(st, g, num_sms);
         else if (epi == AEPI_XIELU) gemm_any_launch<__nv_bfloat16, AEPI_XIELU>(st, g, num_sms);
+        else if (epi == AEPI_RELU2) gemm_any_launch<__nv_bfloat16, AEPI_RELU2>(st, g, num_sms);
         else gemm_any_launch<__nv_bfloat16, AEPI_SWIGLU>(st, g, num_sms);
     }
     AHA_CUDA_CHECK(cudaGetLastError());

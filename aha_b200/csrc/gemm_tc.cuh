@@ -681,12 +681,13 @@ inline void gemm_tc_launch(cudaStream_t st, int epi, const __half* a_hi, const _
 // Grouped launch: A (hi / lo halves, [M, K]) and C rows in g.groups consecutive ranges (g.grp_offsets on the device), tm_w over the stacked
 // [groups * N, K] weights.  The grid covers the worst case of row tiles; the 128 x 128 kernel only.
 inline void gemm_tc_grouped_launch(cudaStream_t st, int epi, const __half* a_hi, const __half* a_lo, const CUtensorMap& tm_w, const GemmTcArgs& g) {
-    AHA_REQUIRE(g.grp_offsets && g.groups >= 1 && (epi == EPI_STORE || epi == EPI_SWIGLU), "gemm_tc: bad grouped launch");
+    AHA_REQUIRE(g.grp_offsets && g.groups >= 1 && (epi == EPI_STORE || epi == EPI_SWIGLU || epi == EPI_ACT), "gemm_tc: bad grouped launch");
     const CUtensorMap tm_hi = make_tmap_f16(a_hi, (uint64_t)g.M, (uint64_t)g.K);
     const CUtensorMap tm_lo = make_tmap_f16(a_lo, (uint64_t)g.M, (uint64_t)g.K);
     const size_t smem = gemm_tc_smem_bytes();
     dim3 grid(ceil_div(g.N, kTcBN), ceil_div(g.M, kTcBM) + g.groups);
     if (epi == EPI_STORE) gemm_tc_kernel<EPI_STORE><<<grid, kTcThreads, smem, st>>>(tm_hi, tm_lo, tm_w, g);
+    else if (epi == EPI_ACT) gemm_tc_kernel<EPI_ACT><<<grid, kTcThreads, smem, st>>>(tm_hi, tm_lo, tm_w, g);
     else gemm_tc_kernel<EPI_SWIGLU><<<grid, kTcThreads, smem, st>>>(tm_hi, tm_lo, tm_w, g);
     AHA_CUDA_CHECK(cudaGetLastError());
 }

@@ -6,6 +6,7 @@
 //                            order never depends on thread timing), every expert's first row, the token row of every ordered assignment
 //                            (the gather index of the first product) and every assignment's place in that order (for the combine)
 //   moe_combine_kernel       y[t] = weight * sum over the token's choices of its experts' output rows
+// With table == nullptr the first kernel only ORDERS assignments whose experts something else chose (moe_router.cuh).
 #pragma once
 #include "common.cuh"
 
@@ -13,7 +14,7 @@ namespace aha {
 
 struct MoeRouteArgs {
     const uint32_t* tokens; int T;
-    const int* table; int table_ld; int V;   // [V][table_ld], the first `top` entries of a row are used
+    const int* table; int table_ld; int V;   // [V][table_ld], the first `top` entries of a row are used; nullptr: expert_of is given (a router chose)
     int top, experts;
     int* expert_of;      // [T * top]
     int* offsets;        // [experts + 1]   (sort)
@@ -31,9 +32,12 @@ static __global__ void __launch_bounds__(1024) moe_table_route_kernel(MoeRouteAr
     for (int e = tid; e < a.experts; e += blockDim.x) cnt[e] = 0;
     __syncthreads();
     for (int i = tid; i < A; i += blockDim.x) {
-        uint32_t tok = a.tokens[i / a.top];
-        if (tok >= (uint32_t)a.V) tok = a.V - 1;
-        int e = a.table[(size_t)tok * a.table_ld + i % a.top];
+        int e;
+        if (a.table) {
+            uint32_t tok = a.tokens[i / a.top];
+            if (tok >= (uint32_t)a.V) tok = a.V - 1;
+            e = a.table[(size_t)tok * a.table_ld + i % a.top];
+        } else e = a.expert_of[i];
         if (e < 0 || e >= a.experts) { *a.error = 1; e = 0; }
         a.expert_of[i] = e;
         if (a.stage) eo[i] = e;

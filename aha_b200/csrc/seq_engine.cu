@@ -16,6 +16,14 @@
 //     "mamba2"     selective state space: convolved x / B / C, scalar decay per head, gate before a grouped norm        (recurrence.cuh, ssm.cuh)
 //     "latent_attention"  softmax attention over one cached latent + one rotated key part per token (YaRN rotary)       (attention_latent.cuh)
 //     "moe"        gated experts chosen by a table row of the token id, grouped matrix products                         (moe_table.cuh)
+// A design may bind a name to a variant of its own ("<architecture>:<name>" is looked up first).  The Lupolorn design (sandwich template
+// without convolution or groups, the embedding table also the output projection) has
+//     "mingru"     elementwise gated recurrence, one fp32 per channel and sequence in the slot pool                      (recurrence_elem.cuh)
+//     "attention"  causal attention with rotary positions (frequencies rescaled band by band), unit-RMS queries and keys, a softmax
+//                  whose denominator holds an extra 1, one sigmoid gate per head                                          (attention_window.cuh)
+//     "latent_attention"  as above without a rotated part: queries through a normed latent of their own, a sliding window
+//     "dense"      W_down relu(W_up x)^2
+//     "moe"        softmax router, the `top` best scores weigh their experts unrenormalised, a shared expert behind a sigmoid gate  (moe_router.cuh)
 // Memory: one free list of 32-token pages serves every layer that owns keys / values (K pages [page][G][32][D], V pages
 // [page][G][32][Dv], fp32); a sequence additionally owns a state slot (recurrent states, convolution tails, sampler state).
 // Precision: the residual stream, norms, gates, recurrent state, scores and softmax are fp32 in both modes; the Linear layers
@@ -33,9 +41,11 @@
 #include "gemm_tc.cuh"
 #include "json.hpp"
 #include "kernels_common.cuh"
+#include "moe_router.cuh"
 #include "moe_table.cuh"
 #include "norm_group.cuh"
 #include "recurrence.cuh"
+#include "recurrence_elem.cuh"
 #include "runtime.cuh"
 #include "sampling.cuh"
 #include "ssm.cuh"
@@ -110,6 +120,7 @@ struct Engine final : SeqEngine {
     };
     std::vector<LayerRec> layers;
     bool sandwich = false;
+    std::string design;            // config.json's "architecture", lower case
     int norm_groups = 1, conv_taps = 0;
     float resid_mult = 1.f, embed_scale = 1.f, logit_scale = 1.f;
     float* final_w = nullptr;      // sandwich: [W] gain of the final norm
@@ -292,8 +303,8 @@ struct Engine final : SeqEngine {
             if (!Wt.has_tmap) { Wt.tmap = make_tmap_f16(Wt.w, (uint64_t)Wt.N, (uint64_t)Wt.K); Wt.has_tmap = true; }   // 16-bit elements: the copy is bitwise
             GemmTcArgs t{};
             t.bias = Wt.b; t.resid = nullptr; t.ldr = 0; t.C = C; t.ldc = ldc; t.M = M; t.N = Wt.N; t.K = Wt.K;
-            t.act = epi == AEPI_XIELU ? ACT_XIELU : ACT_NONE; t.act_a = a0; t.act_b = a1; t.bf16 = 1; t.group_m = std::max(1, c.gemm_group_m);
-            const int e = epi == AEPI_XIELU ? EPI_ACT : (epi == AEPI_SWIGLU ? EPI_SWIGLU : EPI_STORE);
+            t.act = epi == AEPI_XIELU ? ACT_XIELU : (epi == AEPI_RELU2 ? ACT_RELU2 : ACT_NONE); t.act_a = a0; t.act_b = a1; t.bf16 = 1; t.group_m = std::max(1, c.gemm_group_m);
+            const int e = (epi == AEPI_XIELU || epi == AEPI_RELU2) ? EPI_ACT : (epi == AEPI_SWIGLU ? EPI_SWIGLU : EPI_STORE);
             if (c.gemm_pair && Wt.N >= 256 && M >= 1024) gemm_tc3_launch(c.stream, e, hi, lo, Wt.tmap, t, c.num_sms);
             else if (c.gemm_wide && Wt.N >= 256) {
                 if (!Wt.has_tmap256) { Wt.tmap256 = make_tmap_f16_rows(Wt.w, (uint64_t)Wt.N, (uint64_t)Wt.K, 256); Wt.has_tmap256 = true; }
@@ -743,9 +754,21 @@ struct Hgrn2Mixer final : Sublayer {
     }
 };
 
+// What differs between the designs' "attention" mixers; everything else (sizes, window, scale, convolution, biases, cache reuse) comes from the
+// layer's config entry and the checkpoint's tensors.
+struct AttentionFlavor {
+    bool distance_penalty = true;   // score -= 2^(-8 (h + 1) / H) * (i - j)
+    bool rotary = false;            // rotary positions from the layer's "rot" entry, then ...
+    bool unit_qk = false;           // ... every q and k head divided by its own root mean square (instead of whole-projection norms with gains)
+    bool sink = false;              // softmax denominator + 1
+    bool head_gate = false;         // the output gate '.g' has one row per head (else one per output channel, if the tensor exists)
+};
+
 struct WindowAttentionMixer final : Sublayer {
     Engine& E;
-    int H, G, D, Dv, taps = 0, window = 0, kv_from = -1;
+    AttentionFlavor fl;
+    int H, G, D, Dv, taps = 0, window = 0, kv_from = -1, n_freq = 0;
+    float* freq = nullptr;
     float scale = 1.f;
     LinearAny in, out;
     int q_off = 0, k_off = 0, v_off = 0, g_off = -1;
@@ -753,7 +776,7 @@ struct WindowAttentionMixer final : Sublayer {
     size_t tail_stride = 0;
     PagedKV kv;          // own pages, or the owner's when kv_from >= 0
     bool owns_kv = true;
-    WindowAttentionMixer(Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int layer_index) : E(e) {
+    WindowAttentionMixer(Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int layer_index, AttentionFlavor flavor = AttentionFlavor()) : E(e), fl(flavor) {
         H = mx.integer("heads"); G = mx.integer_or("kv_heads", H); D = mx.integer("dim"); Dv = mx.integer_or("vdim", D);
         AHA_REQUIRE(H >= 1 && G >= 1 && H % G == 0, "attention: heads must be a multiple of kv_heads");
         scale = (float)mx.number("scale");
@@ -762,7 +785,7 @@ struct WindowAttentionMixer final : Sublayer {
         AHA_REQUIRE(window >= 0, "attention: mask.size must be positive");
         kv_from = mx.integer_or("kv_from", -1);
         owns_kv = kv_from < 0;
-        const bool gate = wt.has(p + "g");
+        const bool gate = fl.head_gate || wt.has(p + "g");
         std::vector<std::string> names{p + "q"}, biases{p + "q.b"};
         std::vector<int> rows{H * D};
         int col = H * D;
@@ -770,9 +793,27 @@ struct WindowAttentionMixer final : Sublayer {
             k_off = col; names.push_back(p + "k"); biases.push_back(p + "k.b"); rows.push_back(G * D); col += G * D;
             v_off = col; names.push_back(p + "v"); biases.push_back(p + "v.b"); rows.push_back(G * Dv); col += G * Dv;
         }
-        if (gate) { g_off = col; names.push_back(p + "g"); biases.push_back(""); rows.push_back(H * Dv); col += H * Dv; }
-        in = E.load_linear(wt, names, rows, E.W, biases);
+        if (gate) { g_off = col; names.push_back(p + "g"); biases.push_back(""); rows.push_back(fl.head_gate ? H : H * Dv); col += rows.back(); }
+        in = E.load_linear(wt, names, rows, E.W, biases, fl.head_gate ? 32 : 1);      // (a row per head rarely tiles for the tensor cores: zero rows are appended)
         out = E.load_linear(wt, {p + "o"}, {E.W}, H * Dv, {});
+        if (fl.rotary || fl.unit_qk) {
+            AHA_REQUIRE(owns_kv, "attention: a layer with rotary positions owns its keys and values");
+            std::vector<float> fr;
+            if (fl.rotary && mx.has("rot")) {
+                const Json& rot = mx.at("rot");
+                const int dims = rot.integer_or("dims", D);
+                AHA_REQUIRE(dims >= 0 && dims <= D && dims % 2 == 0, "attention: rot.dims must be even and at most dim");
+                if (dims > 0) {
+                    if (rot.has("scaling")) {
+                        const Json& sc = rot.at("scaling");
+                        banded_rotary_frequencies(dims, rot.number("base"), sc.number("factor"), sc.number("low"), sc.number("high"), sc.number("original"), fr);
+                    } else banded_rotary_frequencies(dims, rot.number("base"), 0.0, 1.0, 1.0, 1.0, fr);
+                }
+            }
+            n_freq = (int)fr.size();
+            if (fr.empty()) fr.push_back(0.f);
+            freq = upload(E.c, fr);
+        }
         if (wt.has(p + "q.norm")) q_norm = upload_vec(E.c, wt, p + "q.norm", (size_t)H * D);
         if (owns_kv && wt.has(p + "k.norm")) k_norm = upload_vec(E.c, wt, p + "k.norm", (size_t)G * D);
         if (taps > 1) {
@@ -783,9 +824,11 @@ struct WindowAttentionMixer final : Sublayer {
             tails = E.c.alloc<float>(tail_stride * E.slots);
             AHA_CUDA_CHECK(cudaMemset(tails, 0, tail_stride * E.slots * sizeof(float)));
         }
-        std::vector<float> sl(H);
-        for (int h = 0; h < H; ++h) sl[h] = (float)std::exp2(-8.0 * (double)(h + 1) / (double)H);
-        slopes = upload(E.c, sl);
+        if (fl.distance_penalty) {
+            std::vector<float> sl(H);
+            for (int h = 0; h < H; ++h) sl[h] = (float)std::exp2(-8.0 * (double)(h + 1) / (double)H);
+            slopes = upload(E.c, sl);
+        }
         if (owns_kv) {
             kv.G = G; kv.D = D; kv.Dv = Dv;
             const size_t nk = (size_t)E.num_pages * G * kPage * D, nv = (size_t)E.num_pages * G * kPage * Dv;
@@ -808,23 +851,33 @@ struct WindowAttentionMixer final : Sublayer {
     void run(const StepView& v) override {
         const int T = v.rb.T;
         E.gemm(AEPI_STORE, v.x, E.W, in, E.proj, in.N, T);
-        QkvPrepArgs a{};
-        a.proj = E.proj; a.ld = in.N; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off;
-        a.Cq = H * D; a.Ck = owns_kv ? G * D : 0; a.Cv = owns_kv ? G * Dv : 0;
-        a.taps = taps; a.wq = wq; a.wk = wk; a.wv = wv; a.tails = tails; a.tail_slot_stride = tail_stride;
-        a.q_norm = q_norm; a.k_norm = k_norm; a.eps = E.eps; a.q_out = E.qbuf; a.kv = kv; a.rb = v.rb;
-        E.tic("conv + q/k norm + cache write", 2.0 * T * (a.Cq + a.Ck + a.Cv) * std::max(1, taps), 4.0 * T * (2.0 * a.Cq + 2.0 * a.Ck + 2.0 * a.Cv));
-        E.c.cnt.kernels += qkv_prepare(E.c.stream, a, v.rb.E == T);
-        E.toc();
+        if (fl.rotary || fl.unit_qk) {
+            RotaryPrepArgs a{};
+            a.proj = E.proj; a.ld = in.N; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; a.H = H; a.G = G; a.D = D; a.Dv = Dv;
+            a.freq = freq; a.n_freq = n_freq; a.unit_norm = fl.unit_qk ? 1 : 0; a.eps = E.eps; a.q_out = E.qbuf; a.kv = kv; a.rb = v.rb;
+            E.tic("rotary + q/k unit norm + cache write", 8.0 * T * (H + G) * D, 4.0 * T * (2.0 * H * D + 2.0 * G * D + 2.0 * G * Dv));
+            E.c.cnt.kernels += qk_rotary_prepare(E.c.stream, a);
+            E.toc();
+        } else {
+            QkvPrepArgs a{};
+            a.proj = E.proj; a.ld = in.N; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off;
+            a.Cq = H * D; a.Ck = owns_kv ? G * D : 0; a.Cv = owns_kv ? G * Dv : 0;
+            a.taps = taps; a.wq = wq; a.wk = wk; a.wv = wv; a.tails = tails; a.tail_slot_stride = tail_stride;
+            a.q_norm = q_norm; a.k_norm = k_norm; a.eps = E.eps; a.q_out = E.qbuf; a.kv = kv; a.rb = v.rb;
+            E.tic("conv + q/k norm + cache write", 2.0 * T * (a.Cq + a.Ck + a.Cv) * std::max(1, taps), 4.0 * T * (2.0 * a.Cq + 2.0 * a.Ck + 2.0 * a.Cv));
+            E.c.cnt.kernels += qkv_prepare(E.c.stream, a, v.rb.E == T);
+            E.toc();
+        }
         WindowAttnArgs w{};
         w.q = E.qbuf; w.kv = kv; w.slopes = slopes; w.scale = scale; w.window = window;
-        w.gate = g_off >= 0 ? E.proj + g_off : nullptr; w.gate_ld = in.N; w.out = E.inner; w.H = H; w.rb = v.rb;
+        w.gate = g_off >= 0 ? E.proj + g_off : nullptr; w.gate_ld = in.N; w.gate_per_head = fl.head_gate ? 1 : 0; w.sink = fl.sink ? 1 : 0;
+        w.out = E.inner; w.H = H; w.rb = v.rb;
         w.part = E.opt.seq_impl == 1 ? nullptr : E.attn_part;
         // prompt portions on the tensor cores (one launch pair per entry), everything else -- decoded tokens, short portions, exact mode,
         // other head sizes -- on the CUDA-core kernel, which skips the entries the tensor cores took
         const bool tc = !E.fp32 && E.opt.seq_impl != 1 && D == Dv && (D == 64 || D == 128);
         int tc_tokens = 0;
-        E.tic("window attention", 2.0 * E.prof_pairs(window) * H * (D + Dv), 4.0 * (T * (double)H * (D + Dv) + E.prof_unique(window) * G * (D + Dv)));
+        E.tic(window > 0 ? "window attention" : "causal attention", 2.0 * E.prof_pairs(window) * H * (D + Dv), 4.0 * (T * (double)H * (D + Dv) + E.prof_unique(window) * G * (D + Dv)));
         if (tc)
             for (int e = 0; e < v.rb.E; ++e) {
                 const int n = v.h_ent_start[e + 1] - v.h_ent_start[e], pos0 = v.h_ent_pos0[e];
@@ -837,7 +890,8 @@ struct WindowAttentionMixer final : Sublayer {
                 f.kv0 = window > 0 ? std::max(0, pos0 - window + 1) : 0;      // keys before the first query's window are not staged
                 f.Sq = n; f.Skv = pos0 + n - f.kv0; f.q0 = v.h_ent_start[e]; f.groups = H / G; f.scaling = scale;
                 FlashWindow fw;
-                fw.window = window; fw.slopes = slopes; fw.gate = w.gate; fw.gate_tok_stride = in.N;
+                fw.window = window; fw.slopes = slopes; fw.gate_tok_stride = in.N; fw.sink = w.sink;
+                if (fl.head_gate) fw.gate_head = w.gate; else fw.gate = w.gate;
                 if (D == 64) flash_attn_tc<64>(E.c.stream, f, H, true, E.c.split_buf((flash_tc_ws_halfs<64>(f, H) + 1) / 2), &fw);
                 else flash_attn_tc<128>(E.c.stream, f, H, true, E.c.split_buf((flash_tc_ws_halfs<128>(f, H) + 1) / 2), &fw);
                 E.c.cnt.kernels += 2;
@@ -857,18 +911,21 @@ struct DenseFF final : Sublayer {
     int ff;
     LinearAny up, down;
     float alpha_p = 0.f, alpha_n = 0.f;
-    DenseFF(Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) : E(e) {
+    int act;      // AEPI_XIELU (two learned parameters in '.act') or AEPI_RELU2
+    DenseFF(Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p, int activation = AEPI_XIELU) : E(e), act(activation) {
         ff = cfg.integer("ff");
         up = E.load_linear(wt, {p + "up"}, {ff}, E.W, {});
         down = E.load_linear(wt, {p + "down"}, {E.W}, ff, {});
-        auto a = wt.vec_f32(p + "act", 2);
-        alpha_p = (float)softplus_d(a[0]);
-        alpha_n = (float)(0.5 + softplus_d(a[1]));
+        if (act == AEPI_XIELU) {
+            auto a = wt.vec_f32(p + "act", 2);
+            alpha_p = (float)softplus_d(a[0]);
+            alpha_n = (float)(0.5 + softplus_d(a[1]));
+        }
     }
     int proj_cols() const override { return ff; }
     int inner_cols() const override { return 0; }
     void run(const StepView& v) override {
-        E.gemm(AEPI_XIELU, v.x, E.W, up, E.proj, ff, v.rb.T, alpha_p, alpha_n);
+        E.gemm(act, v.x, E.W, up, E.proj, ff, v.rb.T, alpha_p, alpha_n);
         E.gemm(AEPI_STORE, E.proj, ff, down, v.y, E.W, v.rb.T);
     }
 };
@@ -1000,22 +1057,40 @@ struct Mamba2Mixer final : Sublayer {
 };
 
 // Latent attention (see attention_latent.cuh): the cache holds [latent | rotated key part] per token; a head's query is absorbed through
-// W_uk, its output expanded through W_uv; sigmoid output gate from the mixer's input; causal, ordinary softmax.
+// W_uk, its output expanded through W_uv; causal, ordinary softmax.  By the layer's config entry and tensors: a rotated part (rot_dim > 0,
+// YaRN rotary), queries through a normed latent of their own ('q_rank': q = W_uq norm(W_dq h)) or straight from the input ('.q'), a sliding
+// window ('mask.size'), a sigmoid output gate from the mixer's input ('.g').
 struct LatentAttentionMixer final : Sublayer {
     Engine& E;
-    int H, D, R, Dv, rank;
+    int H, D, R, Dv, rank, q_rank = 0, window = 0;
     float scale, rot_mult = 1.f;
-    LinearAny in, out, uk_t, uv, ukv;
-    bool can_expand = false;
-    int q_off = 0, dkv_off = 0, g_off = 0, n_freq = 0;
-    float *c_norm = nullptr, *freq = nullptr;
+    LinearAny in, out, uq, uk_t, uv, ukv;
+    bool can_expand = false, has_gate = false;
+    int ld = 0, q_off = 0, dkv_off = 0, g_off = 0, n_freq = 0;
+    float *c_norm = nullptr, *q_norm = nullptr, *freq = nullptr;
     PagedKV kv;
     LatentAttentionMixer(Engine& e, const Json& mx, const WeightTable& wt, const std::string& p) : E(e) {
-        H = mx.integer("heads"); D = mx.integer("dim"); R = mx.integer("rot_dim"); Dv = mx.integer("vdim"); rank = mx.integer("kv_rank");
+        H = mx.integer("heads"); D = mx.integer("dim"); R = mx.integer_or("rot_dim", 0); Dv = mx.integer("vdim"); rank = mx.integer("kv_rank");
         AHA_REQUIRE(H >= 1 && D >= 1 && R >= 0 && Dv >= 1 && rank >= 1, "latent attention: bad sizes");
         scale = (float)mx.number("scale");
-        q_off = 0; dkv_off = H * (D + R); g_off = dkv_off + rank + R;
-        in = E.load_linear(wt, {p + "q", p + "dkv", p + "g"}, {H * (D + R), rank + R, H * Dv}, E.W, {}, 32);
+        q_rank = mx.integer_or("q_rank", 0);
+        window = mx.has("mask") ? mx.at("mask").integer("size") : 0;
+        AHA_REQUIRE(q_rank >= 0 && window >= 0, "latent attention: q_rank and mask.size must be positive");
+        has_gate = wt.has(p + "g");
+        {   // one product for everything that reads the mixer's input: [q or its latent | dkv | gate]
+            const int first = q_rank > 0 ? q_rank : H * (D + R);
+            std::vector<std::string> names{p + (q_rank > 0 ? "dq" : "q"), p + "dkv"};
+            std::vector<int> rows{first, rank + R};
+            dkv_off = first; g_off = dkv_off + rank + R;
+            if (has_gate) { names.push_back(p + "g"); rows.push_back(H * Dv); }
+            in = E.load_linear(wt, names, rows, E.W, {}, 32);
+        }
+        ld = in.N;
+        if (q_rank > 0) {      // the expanded queries follow in the same rows
+            uq = E.load_linear(wt, {p + "uq"}, {H * (D + R)}, q_rank, {}, 32);
+            q_norm = E.vec(wt, p + "dq.norm", (size_t)q_rank);
+            q_off = in.N; ld = in.N + uq.N;
+        }
         out = E.load_linear(wt, {p + "o"}, {E.W}, H * Dv, {});
         c_norm = E.vec(wt, p + "dkv.norm", (size_t)rank);
         // W_uk [H * D, rank] transposed head by head: row h * rank + r holds column r of the head's rows
@@ -1062,26 +1137,36 @@ struct LatentAttentionMixer final : Sublayer {
         kv.v = kv.k;
         AHA_CUDA_CHECK(cudaMemset(kv.k, 0, nk * sizeof(float)));
     }
-    int proj_cols() const override { return in.N; }
+    // the most cached rows a prompt portion's expanded form reads: the whole pool, or a step's tokens plus the window before them
+    size_t expand_rows() const { const size_t all = (size_t)E.num_pages * kPage; return window > 0 ? std::min(all, (size_t)E.Tmax + window) : all; }
+    int proj_cols() const override { return ld; }
     int inner_cols() const override { return H * rank; }
     int q_cols() const override { return std::max(H * (rank + R), H * Dv); }
     size_t attn_part_floats() const override { return window_attn_part_floats(H, rank); }
     uint64_t kv_bytes_per_token() const override { return 4ull * (rank + R); }
-    size_t expand_gather_floats() const override { return can_expand ? (size_t)E.num_pages * kPage * (rank + R) : 0; }
-    size_t expand_kv_floats() const override { return can_expand ? (size_t)E.num_pages * kPage * ukv.N : 0; }
+    size_t expand_gather_floats() const override { return can_expand ? expand_rows() * (rank + R) : 0; }
+    size_t expand_kv_floats() const override { return can_expand ? expand_rows() * ukv.N : 0; }
     size_t expand_out_floats() const override { return (size_t)E.Tmax * H * Dv; }
     bool expand_on_tc() const { return can_expand && !E.fp32 && latent_flash_tc_supported(D, R, Dv); }
     size_t expand_split_halfs() const override {
         if (!can_expand || E.fp32) return 0;
-        const size_t smax = (size_t)E.num_pages * kPage;
+        const size_t smax = expand_rows();
         size_t h = smax * rank;                                               // the expansion product's activations
         if (expand_on_tc()) h = std::max(h, latent_flash_tc_ws_halfs(H, E.Tmax, (int)smax, D, R, Dv) / 2);    // the packed q, k, v^T of the longest entry
         return h;
     }
     void run(const StepView& v) override {
-        const int T = v.rb.T, ld = in.N, ldq = H * (rank + R);
+        const int T = v.rb.T, ldq = H * (rank + R);
         cudaStream_t st = E.c.stream;
         E.gemm(AEPI_STORE, v.x, E.W, in, E.proj, ld, T);
+        if (q_rank > 0) {      // q = W_uq norm(W_dq h): the latent is normed in place, the queries land behind the stacked projection
+            E.tic("query latent norm", 4.0 * T * q_rank, 8.0 * T * q_rank);
+            GroupNormArgs n{};
+            n.in = E.proj; n.ld_in = ld; n.w = q_norm; n.eps = E.eps; n.C = q_rank; n.groups = 1; n.out = E.proj; n.ld_out = ld;
+            group_rmsnorm(st, n, T); E.c.cnt.kernels++;
+            E.toc();
+            E.gemm(AEPI_STORE, E.proj, ld, uq, E.proj + q_off, ld, T);
+        }
         E.tic("latent norm + rotary + cache write", 8.0 * T * (rank + (H + 1) * R), 8.0 * T * (rank + (H + 1) * R));
         LatentPrepArgs a{};
         a.proj = E.proj; a.ld = ld; a.q_off = q_off; a.dkv_off = dkv_off; a.H = H; a.D = D; a.R = R; a.rank = rank; a.c_norm = c_norm; a.eps = E.eps;
@@ -1105,12 +1190,13 @@ struct LatentAttentionMixer final : Sublayer {
         }
         if (!all_long) {
             WindowAttnArgs w{};
-            w.q = E.qbuf; w.kv = kv; w.slopes = nullptr; w.scale = scale; w.window = 0; w.gate = nullptr; w.out = E.inner; w.H = H; w.rb = v.rb;
+            w.q = E.qbuf; w.kv = kv; w.slopes = nullptr; w.scale = scale; w.window = window; w.gate = nullptr; w.out = E.inner; w.H = H; w.rb = v.rb;
             w.part = E.opt.seq_impl == 1 ? nullptr : E.attn_part;
             w.skip_from_n = any_long ? kLatentExpandMinTokens : 0;
-            E.tic("latent attention (absorbed)", 2.0 * E.prof_pairs(0) * H * (2.0 * rank + R), 4.0 * (T * (double)H * (2.0 * rank + R) + E.prof_unique(0) * (rank + R)));
-            if (w.part && !any_long && T <= kWinSplitMaxTokens && latent_decode_supported(kv.D, kv.Dv)) E.c.cnt.kernels += latent_decode_attn(st, w, v.span);     // all heads share a block's key rows
-            else E.c.cnt.kernels += window_attn(st, w, v.span);
+            const int span = window > 0 ? std::min(window, v.span) : v.span;
+            E.tic("latent attention (absorbed)", 2.0 * E.prof_pairs(window) * H * (2.0 * rank + R), 4.0 * (T * (double)H * (2.0 * rank + R) + E.prof_unique(window) * (rank + R)));
+            if (w.part && !any_long && T <= kWinSplitMaxTokens && latent_decode_supported(kv.D, kv.Dv)) E.c.cnt.kernels += latent_decode_attn(st, w, span);     // all heads share a block's key rows
+            else E.c.cnt.kernels += window_attn(st, w, span);
             E.toc();
             // o[t][h] = W_uv(h) o_latent[t][h]  (rows of skipped entries are overwritten below)
             GemmAnyArgs g{};
@@ -1119,10 +1205,12 @@ struct LatentAttentionMixer final : Sublayer {
             E.gemm_batched("per-head latent products", AEPI_STORE, g, 2.0 * T * H * rank * Dv, (double)H * rank * Dv * (E.fp32 ? 4 : 2) + 4.0 * T * H * (Dv + rank));
         }
         for (int e = 0; any_long && e < v.rb.E; ++e) {
-            const int n = v.h_ent_start[e + 1] - v.h_ent_start[e], pos0 = v.h_ent_pos0[e], S = pos0 + n;
+            const int n = v.h_ent_start[e + 1] - v.h_ent_start[e], pos0 = v.h_ent_pos0[e];
             if (n < kLatentExpandMinTokens) continue;
+            // with a window nothing before the first query's first visible key is expanded; positions then count from that key
+            const int kv0 = window > 0 ? std::max(0, pos0 - window + 1) : 0, S = pos0 + n - kv0, rel0 = pos0 - kv0;
             E.tic("latent expansion (gather + linear)", 0.0, 8.0 * S * (rank + R));
-            latent_gather_kernel<<<S, 128, 0, st>>>(kv, v.rb.page_tables + (size_t)v.h_ent_slot[e] * v.rb.max_pages, E.lat_gather, S);
+            latent_gather_kernel<<<S, 128, 0, st>>>(kv, v.rb.page_tables + (size_t)v.h_ent_slot[e] * v.rb.max_pages, E.lat_gather, kv0, S);
             E.c.cnt.kernels++;
             E.toc();
             E.gemm(AEPI_STORE, E.lat_gather, rank + R, ukv, E.lat_kv, ukv.N, S);
@@ -1132,9 +1220,9 @@ struct LatentAttentionMixer final : Sublayer {
             f.kx = E.lat_kv; f.ld_k = ukv.N; f.k_head_stride = D;
             f.vx = E.lat_kv + (size_t)H * D; f.ld_v = ukv.N; f.v_head_stride = Dv;
             f.k_rot = E.lat_gather + rank; f.ld_kr = rank + R;
-            f.out = attn_out; f.ld_o = H * Dv; f.t0 = v.h_ent_start[e]; f.n = n; f.pos0 = pos0; f.D = D; f.R = R; f.Dv = Dv; f.scale = scale;
+            f.out = attn_out; f.ld_o = H * Dv; f.t0 = v.h_ent_start[e]; f.n = n; f.pos0 = rel0; f.D = D; f.R = R; f.Dv = Dv; f.scale = scale; f.window = window;
             double pairs = 0;
-            for (int k = 0; k < n; ++k) pairs += pos0 + k + 1;
+            for (int k = 0; k < n; ++k) pairs += window > 0 ? std::min(pos0 + k + 1, window) : pos0 + k + 1;
             if (expand_on_tc()) {
                 E.tic("latent attention (expanded, tcgen05, split fp16)", 2.0 * pairs * H * (D + R + Dv), 4.0 * ((double)n * H * (D + R + Dv) + (double)S * (H * (D + Dv) + R)));
                 E.c.cnt.kernels += latent_flash_tc(st, f, H, E.c.split_buf((latent_flash_tc_ws_halfs(H, n, S, D, R, Dv) + 1) / 2));
@@ -1145,11 +1233,45 @@ struct LatentAttentionMixer final : Sublayer {
             }
             E.toc();
         }
-        E.tic("output gate", 4.0 * T * H * Dv, 12.0 * T * H * Dv);
-        gate_mul_kernel<<<(unsigned)(((size_t)T * H * Dv + 255) / 256), 256, 0, st>>>(attn_out, H * Dv, E.proj + g_off, ld, H * Dv, (size_t)T * H * Dv, 0);
-        E.c.cnt.kernels++;
-        E.toc();
+        if (has_gate) {
+            E.tic("output gate", 4.0 * T * H * Dv, 12.0 * T * H * Dv);
+            gate_mul_kernel<<<(unsigned)(((size_t)T * H * Dv + 255) / 256), 256, 0, st>>>(attn_out, H * Dv, E.proj + g_off, ld, H * Dv, (size_t)T * H * Dv, 0);
+            E.c.cnt.kernels++;
+            E.toc();
+        }
         E.gemm(AEPI_STORE, attn_out, H * Dv, out, v.y, E.W, T);
+    }
+};
+
+// minGRU (see recurrence_elem.cuh): z = sigmoid(W_z h + b_z), candidate from W_x h + b_x, S <- (1 - z) S + z candidate per channel,
+// output W_o (S * silu(W_g h)).  The state is one fp32 per channel and sequence in the slot pool.
+struct MinGruMixer final : Sublayer {
+    Engine& E;
+    int n;
+    LinearAny in, out;
+    float* state = nullptr;
+    MinGruMixer(Engine& e, const Json& mx, const WeightTable& wt, const std::string& p) : E(e) {
+        n = mx.integer("width");
+        AHA_REQUIRE(n >= 1, "mingru: bad width");
+        in = E.load_linear(wt, {p + "z", p + "x", p + "g"}, {n, n, n}, E.W, {p + "z.b", p + "x.b", ""}, 32);
+        out = E.load_linear(wt, {p + "o"}, {E.W}, n, {});
+        state = E.c.alloc<float>((size_t)n * E.slots);
+        AHA_CUDA_CHECK(cudaMemset(state, 0, (size_t)n * E.slots * sizeof(float)));
+    }
+    int proj_cols() const override { return in.N; }
+    int inner_cols() const override { return n; }
+    void run(const StepView& v) override {
+        const int T = v.rb.T;
+        E.gemm(AEPI_STORE, v.x, E.W, in, E.proj, in.N, T);
+        ElemScanArgs a{};
+        a.proj = E.proj; a.ld = in.N; a.z_off = 0; a.c_off = n; a.g_off = 2 * n; a.n = n; a.state = state; a.slot_stride = (size_t)n;
+        a.out = E.inner; a.ld_out = n; a.rb = v.rb;
+        int longest = 0;
+        for (int e = 0; e < v.rb.E; ++e) longest = std::max(longest, v.h_ent_start[e + 1] - v.h_ent_start[e]);
+        E.tic("elementwise recurrence", 12.0 * T * n, 16.0 * T * n + 8.0 * v.rb.E * n);
+        E.c.cnt.kernels += mingru_scan(E.c.stream, a, longest);
+        E.toc();
+        E.gemm(AEPI_STORE, E.inner, n, out, v.y, E.W, T);
     }
 };
 
@@ -1262,6 +1384,134 @@ struct TableMoeFF final : Sublayer {
     }
 };
 
+// Mixture of experts chosen by a router (see moe_router.cuh): scores = softmax(W_router h) over all experts, the `top` best weigh their experts'
+// outputs unrenormalised; expert: W_down act(W_up h) without biases; an optional shared expert of the same form runs for every token and is
+// added times sigmoid(W_sg h).  The router and the shared gate are ONE fp32 product whatever the engine's mode; the experts' matrices are
+// stacked so that the products are batched (decode steps: one row per assignment with its expert's matrix) or grouped (assignments ordered by
+// expert on the device, one launch over all experts; on the tensor cores where the sizes tile).
+struct RoutedMoeFF final : Sublayer {
+    Engine& E;
+    int ff, ffs = 0, experts, top, act;
+    LinearAny up, down, sup, sdown;     // [experts * ff, W], [experts * W, ff]; the shared expert's
+    float* router = nullptr;             // [experts (+ 1), W] fp32: the router's rows, then the shared gate's
+    int n_router = 0, ldl = 0;
+    int* tok_of_assign = nullptr;
+    int* err = nullptr;
+    RoutedMoeFF(Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p, int activation) : E(e), act(activation) {
+        ff = cfg.at("expert").integer("ff"); experts = cfg.at("router").integer("experts"); top = cfg.at("router").integer("top");
+        AHA_REQUIRE(ff >= 1 && experts >= 1 && top >= 1 && top <= experts, "moe: bad sizes");
+        std::vector<std::pair<const aha_tensor_desc*, int>> s1, s2;
+        for (int x = 0; x < experts; ++x) {
+            const std::string q = p + "e" + std::to_string(x) + ".";
+            wt.expect(q + "up", {ff, E.W}); wt.expect(q + "down", {E.W, ff});
+            for (int j = 0; j < ff; ++j) s1.push_back({&wt.get(q + "up"), j});
+            for (int j = 0; j < E.W; ++j) s2.push_back({&wt.get(q + "down"), j});
+        }
+        up = E.load_rows(wt, p + "experts.up", s1, E.W);
+        down = E.load_rows(wt, p + "experts.down", s2, ff);
+        const bool shared = cfg.has("shared") && cfg.at("shared").kind == Json::Obj;
+        if (shared) {
+            ffs = cfg.at("shared").integer("ff");
+            AHA_REQUIRE(ffs >= 1, "moe: bad shared expert size");
+            sup = E.load_linear(wt, {p + "shared.up"}, {ffs}, E.W, {});
+            sdown = E.load_linear(wt, {p + "shared.down"}, {E.W}, ffs, {});
+        }
+        n_router = experts + (shared ? 1 : 0);
+        ldl = n_router + top;      // a token's row: router logits | shared gate | the chosen experts' weights
+        {
+            const std::string key = p + "router (fp32)";
+            auto hit = E.vec_cache.find(key);
+            if (hit != E.vec_cache.end()) router = hit->second;
+            else {
+                std::vector<float> r = wt.vec_f32(p + "router", (size_t)experts * E.W);
+                if (shared) { auto g = wt.vec_f32(p + "shared.sg", (size_t)E.W); r.insert(r.end(), g.begin(), g.end()); }
+                router = E.vec_cache[key] = upload(E.c, r);
+            }
+        }
+        std::vector<int> ta((size_t)kGraphMaxTokens * top);
+        for (size_t i = 0; i < ta.size(); ++i) ta[i] = (int)(i / top);
+        tok_of_assign = upload(E.c, ta);
+        err = E.c.alloc<int>(1);
+        AHA_CUDA_CHECK(cudaMemset(err, 0, sizeof(int)));
+    }
+    int proj_cols() const override { return top * ff + ffs; }           // the experts' hidden rows [T * top, ff], then the shared expert's [T, ffs]
+    int inner_cols() const override { return (top + 1) * E.W; }          // the experts' outputs [T * top, W], then the shared expert's [T, W]
+    int q_cols() const override { return ldl; }
+    size_t route_ints() const override { return 3 * (size_t)E.Tmax * top + experts + 1; }
+    void run(const StepView& v) override {
+        const int T = v.rb.T, A = T * top, W = E.W;
+        cudaStream_t st = E.c.stream;
+        int* expert_of = E.route_buf; int* sorted_tok = expert_of + (size_t)E.Tmax * top; int* place_of = sorted_tok + (size_t)E.Tmax * top; int* offsets = place_of + (size_t)E.Tmax * top;
+        float* logits = E.qbuf;
+        float* hid = E.proj; float* shid = E.proj + (size_t)E.Tmax * top * ff;
+        float* rows_out = E.inner; float* sout = E.inner + (size_t)E.Tmax * top * W;
+        // router (+ shared gate): true fp32 on the CUDA cores in both modes
+        {
+            GemmAnyArgs g{};
+            g.A = v.x; g.lda = W; g.W = router; g.C = logits; g.ldc = ldl; g.M = T; g.N = n_router; g.K = W;
+            E.tic("router", 2.0 * T * n_router * W, 4.0 * ((double)n_router * W + (double)T * (W + n_router)));
+            gemm_any(st, AEPI_STORE, true, g, E.c.num_sms);
+            RouterArgs r{};
+            r.logits = logits; r.ld = ldl; r.T = T; r.experts = experts; r.top = top; r.expert_of = expert_of; r.weights = logits + n_router; r.ld_w = ldl;
+            router_topk(st, r);
+            E.c.cnt.kernels += 2;
+            E.toc();
+        }
+        const bool rows = T <= kGraphMaxTokens && E.opt.seq_impl != 1;      // decode-sized steps: a batch per assignment, no ordering
+        if (!rows) {
+            E.tic("expert routing (order by expert)", 0.0, 16.0 * A);
+            MoeRouteArgs r{};
+            r.tokens = v.rb.tokens; r.T = T; r.table = nullptr; r.table_ld = 0; r.V = E.V; r.top = top; r.experts = experts;
+            r.expert_of = expert_of; r.offsets = offsets; r.sorted_tok = sorted_tok; r.place_of = place_of; r.error = err; r.sort = 1;
+            moe_table_route(st, r); E.c.cnt.kernels++;
+            E.toc();
+        }
+        const double wb = E.fp32 ? 4.0 : 2.0, used = std::min(A, experts);
+        if (!rows && !E.fp32 && E.opt.gemm_impl != 1 && T >= kTcMinRows && W % kTcBK == 0 && ff % kTcBK == 0 && W % 32 == 0) {
+            // both products on the tensor cores, ONE grouped launch each over the ordered rows
+            __half* hi = E.c.split_buf((size_t)A * std::max(W, ff));
+            __half* lo = hi + E.c.split_cap;
+            E.tic("expert linear (grouped, tcgen05, bf16 hi+lo)", 4.0 * A * ff * W, used * 2.0 * ff * W * wb + 4.0 * A * (2.0 * W + 2.0 * ff));
+            gather_split_f32_to_bf16x2_kernel<<<(unsigned)(((size_t)A * W / 4 + 255) / 256), 256, 0, st>>>(v.x, W, sorted_tok, reinterpret_cast<__nv_bfloat16*>(hi), reinterpret_cast<__nv_bfloat16*>(lo), A, W);
+            if (!up.has_tmap) { up.tmap = make_tmap_f16(up.w, (uint64_t)up.N, (uint64_t)up.K); up.has_tmap = true; }
+            if (!down.has_tmap) { down.tmap = make_tmap_f16(down.w, (uint64_t)down.N, (uint64_t)down.K); down.has_tmap = true; }
+            GemmTcArgs t{};
+            t.bias = nullptr; t.resid = nullptr; t.ldr = 0; t.C = hid; t.ldc = ff; t.M = A; t.N = ff; t.K = W; t.bf16 = 1;
+            t.act = act == AEPI_RELU2 ? ACT_RELU2 : ACT_NONE;
+            t.grp_offsets = offsets; t.groups = experts;
+            gemm_tc_grouped_launch(st, EPI_ACT, hi, lo, up.tmap, t);
+            split_f32_to_bf16x2_kernel<<<(unsigned)(((size_t)A * ff / 4 + 255) / 256), 256, 0, st>>>(hid, ff, reinterpret_cast<__nv_bfloat16*>(hi), reinterpret_cast<__nv_bfloat16*>(lo), A, ff);
+            t.C = rows_out; t.ldc = W; t.N = W; t.K = ff; t.act = ACT_NONE;
+            gemm_tc_grouped_launch(st, EPI_STORE, hi, lo, down.tmap, t);
+            E.c.cnt.kernels += 4;
+            E.toc();
+        } else {
+            GemmAnyArgs g{};
+            g.A = v.x; g.lda = W; g.W = up.w; g.C = hid; g.ldc = ff; g.N = ff; g.K = W; g.w_bs = (size_t)ff * W;
+            if (rows) { g.M = 1; g.batch = A; g.a_index = tok_of_assign; g.a_bs = (size_t)W; g.c_bs = (size_t)ff; g.w_index = expert_of; }
+            else { g.M = A; g.batch = experts; g.row_offsets = offsets; g.a_gather = sorted_tok; }
+            E.gemm_batched(rows ? "expert linear (decode rows)" : "expert linear (grouped, CUDA cores)", act, g, 2.0 * A * ff * W, used * ff * W * wb + 4.0 * A * (W + ff));
+            GemmAnyArgs d{};
+            d.A = hid; d.lda = ff; d.W = down.w; d.C = rows_out; d.ldc = W; d.N = W; d.K = ff; d.w_bs = (size_t)W * ff;
+            if (rows) { d.M = 1; d.batch = A; d.a_bs = (size_t)ff; d.c_bs = (size_t)W; d.w_index = expert_of; }
+            else { d.M = A; d.batch = experts; d.row_offsets = offsets; }
+            E.gemm_batched(rows ? "expert linear (decode rows)" : "expert linear (grouped, CUDA cores)", AEPI_STORE, d, 2.0 * A * ff * W, used * ff * W * wb + 4.0 * A * (W + ff));
+        }
+        if (ffs > 0) {
+            E.gemm(act, v.x, W, sup, shid, ffs, T);
+            E.gemm(AEPI_STORE, shid, ffs, sdown, sout, W, T);
+        }
+        E.tic("expert combine", 2.0 * (A + T) * W, 4.0 * (A + 2.0 * T) * W);
+        WeightedCombineArgs cb{};
+        cb.rows = rows_out; cb.place_of = rows ? nullptr : place_of; cb.weights = logits + n_router; cb.ld_w = ldl;
+        cb.shared = ffs > 0 ? sout : nullptr; cb.gate = logits + experts; cb.ld_gate = ldl; cb.y = v.y; cb.C = W; cb.top = top; cb.total = (size_t)T * W;
+        moe_weighted_combine_kernel<<<(unsigned)((cb.total + 255) / 256), 256, 0, st>>>(cb);
+        E.c.cnt.kernels++;
+        AHA_CUDA_CHECK(cudaGetLastError());
+        E.toc();
+    }
+};
+
 using MixerFactory = std::function<std::unique_ptr<Sublayer>(Engine&, const Json&, const WeightTable&, const std::string&, int)>;
 const std::map<std::string, MixerFactory>& mixer_registry() {
     static const std::map<std::string, MixerFactory> r = {
@@ -1270,14 +1520,28 @@ const std::map<std::string, MixerFactory>& mixer_registry() {
         {"gla", [](Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int) { return std::unique_ptr<Sublayer>(new GlaMixer(e, mx, wt, p)); }},
         {"mamba2", [](Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int) { return std::unique_ptr<Sublayer>(new Mamba2Mixer(e, mx, wt, p)); }},
         {"latent_attention", [](Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int) { return std::unique_ptr<Sublayer>(new LatentAttentionMixer(e, mx, wt, p)); }},
+        {"mingru", [](Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int) { return std::unique_ptr<Sublayer>(new MinGruMixer(e, mx, wt, p)); }},
+        {"lupolorn:attention", [](Engine& e, const Json& mx, const WeightTable& wt, const std::string& p, int l) {
+             AttentionFlavor f;
+             f.distance_penalty = false; f.rotary = true; f.unit_qk = true; f.sink = true; f.head_gate = true;
+             return std::unique_ptr<Sublayer>(new WindowAttentionMixer(e, mx, wt, p, l, f));
+         }},
     };
     return r;
+}
+// "<design>:<name>" if the design binds the name to a variant of its own, else "<name>"
+template <typename M>
+typename M::const_iterator find_for_design(const M& reg, const std::string& design, const std::string& name) {
+    auto it = reg.find(design + ":" + name);
+    return it != reg.end() ? it : reg.find(name);
 }
 using FFFactory = std::function<std::unique_ptr<Sublayer>(Engine&, const Json&, const WeightTable&, const std::string&)>;
 const std::map<std::string, FFFactory>& ff_registry() {
     static const std::map<std::string, FFFactory> r = {
         {"dense", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) { return std::unique_ptr<Sublayer>(new DenseFF(e, cfg, wt, p)); }},
         {"moe", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) { return std::unique_ptr<Sublayer>(new TableMoeFF(e, cfg, wt, p)); }},
+        {"lupolorn:dense", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) { return std::unique_ptr<Sublayer>(new DenseFF(e, cfg, wt, p, AEPI_RELU2)); }},
+        {"lupolorn:moe", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) { return std::unique_ptr<Sublayer>(new RoutedMoeFF(e, cfg, wt, p, AEPI_RELU2)); }},
     };
     return r;
 }
@@ -1298,7 +1562,8 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
     // the layer template
     std::string arch = cfg.string_or("architecture", "");
     for (auto& ch : arch) ch = (char)std::tolower((unsigned char)ch);
-    e.sandwich = arch == "gatuzen";
+    e.design = arch;
+    e.sandwich = arch == "gatuzen" || arch == "lupolorn";      // (Lupolorn: the same frame without groups, convolution or multiplier)
     // the runs: layers before the loop once, the loop's span `times` times, the rest once
     std::vector<std::pair<int, int>> runs;      // (layer, pass it opens or -1)
     {
@@ -1333,7 +1598,7 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
     e.Tmax = std::max(1, opt.max_step_tokens);
     e.Rmax = std::min(e.Tmax, 128);
     e.embed = e.load_linear(wt, {"embed"}, {e.V}, e.W, {}).w;
-    e.head = e.load_linear(wt, {"head"}, {e.V}, e.W, {});
+    e.head = e.load_linear(wt, {wt.has("head") ? "head" : "embed"}, {e.V}, e.W, {});      // no 'head' tensor: the embedding table is the output projection
     if (e.sandwich) e.final_w = e.vec(wt, "final.norm", (size_t)e.W);
     else e.final_gain = upload_scalar(e, wt, "final.norm");
     int proj_cols = 1, inner_cols = 1, q_cols = 1;
@@ -1343,7 +1608,7 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
         const Json& ly = ls.arr[l];
         const std::string p = "l" + std::to_string(l) + ".";
         const std::string type = ly.string_or("type", "");
-        auto it = mixer_registry().find(type);
+        auto it = find_for_design(mixer_registry(), e.design, type);
         AHA_REQUIRE(it != mixer_registry().end(), "config.json: layer " + std::to_string(l) + " has an unknown mixer type '" + type + "'");
         Engine::LayerRec rec;
         rec.mixer = it->second(e, ly.at("mixer"), wt, p + "mix.", l);
@@ -1360,10 +1625,10 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
             rec.pre1 = e.vec(wt, p + "norm1", (size_t)e.W); rec.post1 = e.vec(wt, p + "norm1b", (size_t)e.W);
             conv_state(p + "canon1", rec.conv1, rec.tails1);
         } else rec.gain1 = upload_scalar(e, wt, p + "norm1");
-        if (ly.has("mlp")) {
+        if (ly.has("mlp") && ly.at("mlp").kind == Json::Obj) {
             const Json& ml = ly.at("mlp");
             const std::string kind = ml.string_or("kind", "");
-            auto jt = ff_registry().find(kind);
+            auto jt = find_for_design(ff_registry(), e.design, kind);
             AHA_REQUIRE(jt != ff_registry().end(), "config.json: layer " + std::to_string(l) + " has an unknown feed-forward kind '" + kind + "'");
             rec.ff = jt->second(e, ml, wt, p + "mlp.");
             if (e.sandwich) {
