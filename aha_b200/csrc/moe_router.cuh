@@ -2,6 +2,8 @@
 // `top` largest scores name a token's experts and weigh their outputs as they are (no renormalisation over the chosen ones).  A shared
 // expert that every token runs is added behind a sigmoid gate, one number per token.
 //
+//   router_fused_kernel          router product (fp32) + softmax + choice in one launch, see below; the two kernels after it serve sizes whose rows do
+//                                not fit shared memory (the product is then a separate launch)
 //   router_topk_kernel           a warp per token: softmax over the logits (fp32), then `top` rounds of arg-max (the earlier expert wins
 //                                among equal scores), writing assignment a = token * top + choice -> expert and its weight
 //   moe_weighted_combine_kernel  y[t] = sum_k weight[t][k] * rows[place(t, k)] + sigmoid(gate[t]) * shared[t]
@@ -58,6 +60,109 @@ inline void router_topk(cudaStream_t st, const RouterArgs& a) {
     const size_t smem = (size_t)kRouterWarps * a.experts * sizeof(float);
     AHA_REQUIRE(smem <= 48 * 1024, "router: too many experts for the selection kernel");
     router_topk_kernel<<<ceil_div(a.T, kRouterWarps), 32 * kRouterWarps, smem, st>>>(a);
+    AHA_CUDA_CHECK(cudaGetLastError());
+}
+
+// The router product, the softmax and the choice in ONE launch: a block owns TOK tokens, keeps their rows in shared memory, a warp forms one
+// output (an expert's logit, or the shared gate's) for all of them at a time from a single pass over that weight row, then warp r ranks token r.
+// A token's sums run in an order that depends on K only, so its logits are the same whatever else is in the batch and whatever TOK is.
+struct RouterFusedArgs {
+    const float* x; int ldx;         // [T, K] what the router reads
+    const float* w;                  // [n_out, K] fp32: the experts' rows, then (n_out = experts + 1) the shared gate's
+    int T, K, experts, n_out, top;
+    float* logits; int ld;           // [T, ld]: n_out logits, then the `top` weights of the chosen experts
+    int* expert_of;                  // [T * top]
+};
+
+template <int TOK>
+static __global__ void __launch_bounds__(256) router_fused_kernel(RouterFusedArgs a) {
+    extern __shared__ __align__(16) float rf_sm[];
+    float* xs = rf_sm;                               // [TOK][K]
+    float* lg = rf_sm + (size_t)TOK * a.K;           // [TOK][n_out]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, t0 = blockIdx.x * TOK, nt = min(TOK, a.T - t0);
+    const bool vec = (a.K & 3) == 0 && (a.ldx & 3) == 0;
+    for (int r = 0; r < TOK; ++r) {
+        if (r < nt) {
+            const float* src = a.x + (size_t)(t0 + r) * a.ldx;
+            if (vec) for (int k = tid * 4; k < a.K; k += 1024) *reinterpret_cast<float4*>(xs + (size_t)r * a.K + k) = *reinterpret_cast<const float4*>(src + k);
+            else for (int k = tid; k < a.K; k += 256) xs[(size_t)r * a.K + k] = src[k];
+        } else for (int k = tid; k < a.K; k += 256) xs[(size_t)r * a.K + k] = 0.f;
+    }
+    __syncthreads();
+    for (int e = warp; e < a.n_out; e += 8) {
+        const float* wr = a.w + (size_t)e * a.K;
+        float acc[TOK];
+#pragma unroll
+        for (int r = 0; r < TOK; ++r) acc[r] = 0.f;
+        if (vec) {
+#pragma unroll(TOK == 1 ? 8 : 4)      // a row is a few kilobytes: most of its loads are in flight together
+            for (int k = lane * 4; k < a.K; k += 128) {
+                const float4 w4 = *reinterpret_cast<const float4*>(wr + k);
+#pragma unroll
+                for (int r = 0; r < TOK; ++r) {
+                    const float4 x4 = *reinterpret_cast<const float4*>(xs + (size_t)r * a.K + k);
+                    acc[r] = fmaf(x4.w, w4.w, fmaf(x4.z, w4.z, fmaf(x4.y, w4.y, fmaf(x4.x, w4.x, acc[r]))));
+                }
+            }
+        } else {
+            for (int k = lane; k < a.K; k += 32) {
+                const float wv = wr[k];
+#pragma unroll
+                for (int r = 0; r < TOK; ++r) acc[r] = fmaf(xs[(size_t)r * a.K + k], wv, acc[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < TOK; ++r) {
+            const float v = warp_sum(acc[r]);
+            if (lane == 0 && r < nt) { lg[r * a.n_out + e] = v; a.logits[(size_t)(t0 + r) * a.ld + e] = v; }
+        }
+    }
+    __syncthreads();
+    for (int r = warp; r < nt; r += 8) {
+        float* s = lg + (size_t)r * a.n_out;
+        const int t = t0 + r;
+        float mx = -INFINITY;
+        for (int e = lane; e < a.experts; e += 32) mx = fmaxf(mx, s[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < a.experts; e += 32) { s[e] = expf(s[e] - mx); sum += s[e]; }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        __syncwarp();
+        for (int k = 0; k < a.top; ++k) {
+            float best = -1.f; int arg = a.experts;
+            for (int e = lane; e < a.experts; e += 32)
+                if (s[e] > best) { best = s[e]; arg = e; }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, off);
+                if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+            }
+            if (lane == 0) {
+                a.expert_of[(size_t)t * a.top + k] = arg;
+                a.logits[(size_t)t * a.ld + a.n_out + k] = best * inv;
+                s[arg] = -2.f;
+            }
+            __syncwarp();
+        }
+    }
+}
+
+inline size_t router_fused_smem(int tok, int K, int n_out) { return (size_t)tok * (K + n_out) * sizeof(float); }
+inline bool router_fused_supported(int K, int n_out) { return router_fused_smem(8, K, n_out) <= 200 * 1024; }
+
+// decode-sized steps give every token a block of its own (the weight rows are then read once per token, which a few tokens can afford)
+inline void router_fused(cudaStream_t st, const RouterFusedArgs& a) {
+    if (a.T == 0) return;
+    static bool attr = false;
+    if (!attr) {
+        AHA_CUDA_CHECK(cudaFuncSetAttribute(router_fused_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        AHA_CUDA_CHECK(cudaFuncSetAttribute(router_fused_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr = true;
+    }
+    if (a.T <= 8) router_fused_kernel<1><<<a.T, 256, router_fused_smem(1, a.K, a.n_out), st>>>(a);
+    else router_fused_kernel<8><<<ceil_div(a.T, 8), 256, router_fused_smem(8, a.K, a.n_out), st>>>(a);
     AHA_CUDA_CHECK(cudaGetLastError());
 }
 

@@ -5,6 +5,7 @@
 //                          arguments: gathered rows (the rows whose logits are wanted), a value formed on the way
 //                          (in + skip_w[channel / skip_span] * skip) * silu(gate) -- a state-space layer's D x term and output gate --,
 //                          and the residual update  out += mult * normed  (post-norm of a sublayer) instead of a store.
+//   post_pre_norm_kernel   the residual update after a sublayer and the norm before the next one in one launch
 //   short_conv_kernel      causal convolution over time on every channel, y_t = sum_j w[c][j] u_{t - taps + 1 + j} (+ bias) (silu) (+ u_t);
 //                          the taps - 1 inputs before a step are the sequence's state ("tail") in its slot, zeros before position 0.
 //                          An entry of one token moves its tail along in the same launch; short_conv_tail_kernel does it for longer entries.
@@ -71,6 +72,40 @@ inline void group_rmsnorm(cudaStream_t st, const GroupNormArgs& a, int rows) {
     const int threads = std::min(1024, std::max(64, (rows <= 8 ? (n / 2 + 31) : (n / 4 + 31)) / 32 * 32));
     group_rmsnorm_kernel<<<dim3(rows, a.groups), threads, 0, st>>>(a);
     AHA_CUDA_CHECK(cudaGetLastError());
+}
+
+// The end of one sublayer and the start of the next in ONE launch (ungrouped norms, nothing between them):
+//     x += mult * rms_norm(y) * w_post;     h = rms_norm(x) * w_pre
+// One block per row; a thread rereads only what it wrote itself.
+struct PostPreNormArgs {
+    const float* y;            // [T, C] sublayer output
+    float* x;                  // [T, C] residual stream, updated in place
+    const float* w_post;       // [C]
+    const float* w_pre;        // [C]
+    float* h;                  // [T, C] what the next sublayer reads
+    float eps, mult;
+    int C;
+};
+
+static __global__ void post_pre_norm_kernel(PostPreNormArgs a) {
+    __shared__ float red[32];
+    const size_t r = blockIdx.x;
+    const float* __restrict__ y = a.y + r * a.C;
+    float* x = a.x + r * a.C;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < a.C; c += blockDim.x) ss = fmaf(y[c], y[c], ss);
+    ss = block_sum(ss, red);
+    const float sc = a.mult / sqrtf(ss / (float)a.C + a.eps);
+    float s2 = 0.f;
+    for (int c = threadIdx.x; c < a.C; c += blockDim.x) {
+        const float v = x[c] + y[c] * sc * a.w_post[c];
+        x[c] = v;
+        s2 = fmaf(v, v, s2);
+    }
+    s2 = block_sum(s2, red);
+    const float sc2 = 1.0f / sqrtf(s2 / (float)a.C + a.eps);
+    float* h = a.h + r * a.C;
+    for (int c = threadIdx.x; c < a.C; c += blockDim.x) h[c] = x[c] * sc2 * a.w_pre[c];
 }
 
 constexpr int kShortConvMaxTaps = 16;

@@ -529,6 +529,7 @@ struct Engine final : SeqEngine {
                      float* logits_out, const std::vector<size_t>* want_out) {
         cudaStream_t st = c.stream;
         const int T = rb.T;
+        pre_ready = nullptr;
         if (any_fb) { feedback_tokens_kernel<<<ceil_div(T, 256), 256, 0, st>>>(reinterpret_cast<uint32_t*>(d_meta), d_fb, d_states, T); c.cnt.kernels++; }
         if (fp32) embed_gather_any_kernel<float><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const float*>(embed), x, W, V, embed_scale);
         else embed_gather_any_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const __nv_bfloat16*>(embed), x, W, V, embed_scale);
@@ -541,13 +542,16 @@ struct Engine final : SeqEngine {
                 if (Ly.pass >= 0) {
                     add_row_vector_kernel<<<(unsigned)(((size_t)T * W + 255) / 256), 256, 0, st>>>(x, loop_step + (size_t)Ly.pass * W, W, (size_t)T * W); c.cnt.kernels++;
                 }
+                // (the norm before a sublayer rides with the residual update before it where nothing stands between the two)
+                const LayerRec* nx = l + 1 < L ? &layers[l + 1] : nullptr;
+                const float* next_pre = nx && nx->pass < 0 && !nx->conv1 ? nx->pre1 : nullptr;
                 v.x = sublayer_input(rb, Ly.pre1, Ly.conv1, Ly.tails1);
                 Ly.mixer->run(v);
-                sublayer_output(T, Ly.post1);
+                sublayer_output(T, Ly.post1, Ly.ff ? (Ly.conv2 ? nullptr : Ly.pre2) : next_pre);
                 if (Ly.ff) {
                     v.x = sublayer_input(rb, Ly.pre2, Ly.conv2, Ly.tails2);
                     Ly.ff->run(v);
-                    sublayer_output(T, Ly.post2);
+                    sublayer_output(T, Ly.post2, next_pre);
                 }
                 if (trace) AHA_CUDA_CHECK(cudaMemcpyAsync(trace_buf + (size_t)l * Tmax * W, x, (size_t)T * W * sizeof(float), cudaMemcpyDeviceToDevice, st));
                 continue;
@@ -602,6 +606,8 @@ struct Engine final : SeqEngine {
     const float* sublayer_input(const RaggedBatch& rb, const float* gain, const float* conv_w, float* tails) {
         cudaStream_t st = c.stream;
         const int T = rb.T;
+        if (pre_ready == gain && !conv_w) { pre_ready = nullptr; return hnorm; }      // formed by the launch that ended the sublayer before
+        pre_ready = nullptr;
         const size_t tail_stride = (size_t)std::max(0, conv_taps - 1) * W;
         tic("norm + input convolution", (2.0 * conv_taps + 4.0) * T * W, 4.0 * T * W * (conv_w ? 4.0 : 2.0));
         const float* res;
@@ -632,7 +638,18 @@ struct Engine final : SeqEngine {
         return res;
     }
     // ... and what it leaves: x += m * group norm(y) * gain
-    void sublayer_output(int T, const float* gain) {
+    const float* pre_ready = nullptr;      // the gain of the pre-norm whose result hnorm already holds
+    void sublayer_output(int T, const float* gain, const float* next_pre = nullptr) {
+        if (next_pre && norm_groups == 1 && !out_src) {
+            tic("norm + residual + next norm", 8.0 * T * W, 20.0 * T * W);
+            PostPreNormArgs a{};
+            a.y = y; a.x = x; a.w_post = gain; a.w_pre = next_pre; a.h = hnorm; a.eps = eps; a.mult = resid_mult; a.C = W;
+            post_pre_norm_kernel<<<T, T <= 8 ? std::min(1024, std::max(128, (W / 2 + 31) / 32 * 32)) : 256, 0, c.stream>>>(a);
+            c.cnt.kernels++;
+            pre_ready = next_pre;
+            toc();
+            return;
+        }
         tic("norm + residual", 4.0 * T * W, 12.0 * T * W);
         GroupNormArgs n{};
         n.in = y; n.ld_in = W; n.w = gain; n.eps = eps; n.C = W; n.groups = norm_groups; n.out = x; n.ld_out = W; n.mult = resid_mult; n.add = 1;
@@ -1269,7 +1286,7 @@ struct MinGruMixer final : Sublayer {
         int longest = 0;
         for (int e = 0; e < v.rb.E; ++e) longest = std::max(longest, v.h_ent_start[e + 1] - v.h_ent_start[e]);
         E.tic("elementwise recurrence", 12.0 * T * n, 16.0 * T * n + 8.0 * v.rb.E * n);
-        E.c.cnt.kernels += mingru_scan(E.c.stream, a, longest);
+        E.c.cnt.kernels += mingru_scan(E.c.stream, a, longest, E.c.num_sms);
         E.toc();
         E.gemm(AEPI_STORE, E.inner, n, out, v.y, E.W, T);
     }
@@ -1446,17 +1463,22 @@ struct RoutedMoeFF final : Sublayer {
         float* hid = E.proj; float* shid = E.proj + (size_t)E.Tmax * top * ff;
         float* rows_out = E.inner; float* sout = E.inner + (size_t)E.Tmax * top * W;
         // router (+ shared gate): true fp32 on the CUDA cores in both modes
-        {
+        E.tic("router", 2.0 * T * n_router * W, 4.0 * ((double)n_router * W + (double)T * (W + n_router)));
+        if (router_fused_supported(W, n_router)) {      // product, softmax and choice in one launch
+            RouterFusedArgs r{};
+            r.x = v.x; r.ldx = W; r.w = router; r.T = T; r.K = W; r.experts = experts; r.n_out = n_router; r.top = top; r.logits = logits; r.ld = ldl; r.expert_of = expert_of;
+            router_fused(st, r);
+            E.c.cnt.kernels++;
+        } else {
             GemmAnyArgs g{};
             g.A = v.x; g.lda = W; g.W = router; g.C = logits; g.ldc = ldl; g.M = T; g.N = n_router; g.K = W;
-            E.tic("router", 2.0 * T * n_router * W, 4.0 * ((double)n_router * W + (double)T * (W + n_router)));
             gemm_any(st, AEPI_STORE, true, g, E.c.num_sms);
             RouterArgs r{};
             r.logits = logits; r.ld = ldl; r.T = T; r.experts = experts; r.top = top; r.expert_of = expert_of; r.weights = logits + n_router; r.ld_w = ldl;
             router_topk(st, r);
             E.c.cnt.kernels += 2;
-            E.toc();
         }
+        E.toc();
         const bool rows = T <= kGraphMaxTokens && E.opt.seq_impl != 1;      // decode-sized steps: a batch per assignment, no ordering
         if (!rows) {
             E.tic("expert routing (order by expert)", 0.0, 16.0 * A);

@@ -330,7 +330,7 @@ def make_malasun(cfg, seed=0, fast=False):
 
 
 def make_weights(kind, cfg, seed=0):
-    return {"qwen3": make_qwen3, "qwen3vl": make_qwen3vl, "qwen3_asr": make_qwen3_asr, "malasun": make_malasun, "gatuzen": make_gatuzen}[kind](cfg, seed)
+    return {"qwen3": make_qwen3, "qwen3vl": make_qwen3vl, "qwen3_asr": make_qwen3_asr, "malasun": make_malasun, "gatuzen": make_gatuzen, "lupolorn": make_lupolorn}[kind](cfg, seed)
 
 
 # ----------------------------------------------------------------------------- synthetic inputs
@@ -529,4 +529,114 @@ def make_gatuzen(cfg, seed=0, fast=False):
                 lin(q + "gate", ff, W); lin(q + "up", ff, W); lin(q + "down", W, ff)
             tb = np.stack([rng.permutation(E)[:top] for _ in range(V)]).astype(np.float32)
             w[p + "mlp.table"] = tb
+    return w
+
+
+# ----------------------------------------------------------------------------- Lupolorn (layered engine, sandwich template without groups / convolution)
+def lupolorn_config(layers, width=64, vocab=96, eps=1e-5, embed_scale=1.0):
+    """config.json of a Lupolorn model.  layers: list of dicts with "type" and the mixer's sizes,
+         {"type": "mingru", "width"}
+         {"type": "attention", "heads", "kv_heads", "dim", "vdim", "scale", "rot_dims", "base", "scaling": None | {"factor", "low", "high", "original"}}
+         {"type": "latent_attention", "heads", "dim", "vdim", "kv_rank", "q_rank", "window", "scale"}
+       each with "ff": None | int (dense) | {"experts", "top", "ff", "shared": None | int}."""
+    out = []
+    for ly in layers:
+        t = ly["type"]
+        if t == "mingru":
+            mx = {"width": ly["width"]}
+        elif t == "attention":
+            rot = {"base": float(ly.get("base", 10000.0)), "dims": ly.get("rot_dims", ly["dim"])}
+            if ly.get("scaling"):
+                rot["scaling"] = dict(ly["scaling"])
+            mx = {"heads": ly["heads"], "kv_heads": ly.get("kv_heads", ly["heads"]), "dim": ly["dim"], "vdim": ly.get("vdim", ly["dim"]), "rot": rot,
+                  "scale": float(ly.get("scale", ly["dim"] ** -0.5))}
+        elif t == "latent_attention":
+            mx = {"heads": ly["heads"], "dim": ly["dim"], "vdim": ly["vdim"], "kv_rank": ly["kv_rank"], "q_rank": ly["q_rank"], "mask": {"size": ly["window"]},
+                  "scale": float(ly.get("scale", ly["dim"] ** -0.5))}
+        else:
+            raise ValueError(t)
+        ff = ly.get("ff")
+        if ff is None:
+            mlp = None
+        elif isinstance(ff, dict):
+            mlp = {"kind": "moe", "expert": {"ff": ff["ff"]}, "router": {"experts": ff["experts"], "top": ff["top"]}}
+            if ff.get("shared"):
+                mlp["shared"] = {"ff": ff["shared"]}
+        else:
+            mlp = {"kind": "dense", "ff": int(ff)}
+        out.append({"type": t, "mixer": mx, "mlp": mlp})
+    return {"architecture": "Lupolorn", "layers": out, "norm": {"eps": eps}, "embedding": {"scale": embed_scale}, "vocab": vocab, "width": width}
+
+
+def lupolorn_shape(width, n_layers, heads, kv_heads, head_dim, ff, experts, top, expert_ff, vocab=32000, kv_rank=256, q_rank=512, window=1024):
+    """A layer list of the sizes a served model would have: attention, minGRU, latent-attention and attention layers in turn, a dense feed-forward
+    on the even layers and routed experts with a shared expert on the odd ones."""
+    layers = []
+    for i in range(n_layers):
+        k = i % 4
+        f = ff if i % 2 == 0 else {"experts": experts, "top": top, "ff": expert_ff, "shared": expert_ff}
+        if k == 1:
+            layers.append({"type": "mingru", "width": width, "ff": f})
+        elif k == 2:
+            layers.append({"type": "latent_attention", "heads": heads, "dim": head_dim, "vdim": head_dim, "kv_rank": kv_rank, "q_rank": q_rank, "window": window, "ff": f})
+        else:
+            layers.append({"type": "attention", "heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "rot_dims": head_dim, "base": 5e5,
+                           "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}, "ff": f})
+    return lupolorn_config(layers, width=width, vocab=vocab, eps=1e-6, embed_scale=float(np.sqrt(width)))
+
+
+def make_lupolorn(cfg, seed=0, fast=False):
+    """Random weights under the checkpoint's tensor names, all bfloat16 (`_lib.BF16`-tagged bit patterns)."""
+    rng = np.random.default_rng(seed)
+    w = {}
+
+    def rnd(*shape, std=1.0):
+        if fast:
+            a = rng.random(int(np.prod(shape)), dtype=np.float32)
+            a -= np.float32(0.5)
+            a *= np.float32(std * 3.4641016)
+        else:
+            a = rng.standard_normal(int(np.prod(shape)), dtype=np.float32) * np.float32(std)
+        return a.reshape(shape)
+
+    def put(name, a):
+        w[name] = _bf16_round(a)
+
+    def lin(name, out_f, in_f, gain=1.0):
+        put(name, rnd(out_f, in_f, std=gain / np.sqrt(in_f)))
+
+    W, V = cfg["width"], cfg["vocab"]
+    put("embed", rnd(V, W, std=1.0 / max(1.0, cfg["embedding"]["scale"])))
+    put("final.norm", 1.0 + 0.2 * rnd(W))
+    for i, ly in enumerate(cfg["layers"]):
+        p, mx, t = "l%d." % i, ly["mixer"], ly["type"]
+        for nm in ("norm1", "norm1b"):
+            put(p + nm, 1.0 + 0.2 * rnd(W))
+        if t == "mingru":
+            n = mx["width"]
+            lin(p + "mix.z", n, W, 2.0); lin(p + "mix.x", n, W, 2.0); lin(p + "mix.g", n, W); lin(p + "mix.o", W, n)
+            put(p + "mix.z.b", rnd(n, std=1.0)); put(p + "mix.x.b", rnd(n, std=0.5))
+        elif t == "attention":
+            H, G, D, Dv = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+            lin(p + "mix.q", H * D, W, 2.0); lin(p + "mix.k", G * D, W, 2.0); lin(p + "mix.v", G * Dv, W)
+            lin(p + "mix.g", H, W, 2.0); lin(p + "mix.o", W, H * Dv)
+        else:
+            H, D, Dv, rank, qr = mx["heads"], mx["dim"], mx["vdim"], mx["kv_rank"], mx["q_rank"]
+            lin(p + "mix.dq", qr, W); put(p + "mix.dq.norm", 1.0 + 0.2 * rnd(qr)); lin(p + "mix.uq", H * D, qr, 2.0)
+            lin(p + "mix.dkv", rank, W); put(p + "mix.dkv.norm", 1.0 + 0.2 * rnd(rank))
+            lin(p + "mix.uk", H * D, rank, 2.0); lin(p + "mix.uv", H * Dv, rank); lin(p + "mix.o", W, H * Dv)
+        ml = ly.get("mlp")
+        if ml:
+            for nm in ("norm2", "norm2b"):
+                put(p + nm, 1.0 + 0.2 * rnd(W))
+            if ml["kind"] == "dense":
+                lin(p + "mlp.up", ml["ff"], W); lin(p + "mlp.down", W, ml["ff"])
+            else:
+                ff, E = ml["expert"]["ff"], ml["router"]["experts"]
+                for e in range(E):
+                    lin(p + "mlp.e%d.up" % e, ff, W); lin(p + "mlp.e%d.down" % e, W, ff)
+                lin(p + "mlp.router", E, W, 3.0)
+                if ml.get("shared"):
+                    fs = ml["shared"]["ff"]
+                    lin(p + "mlp.shared.up", fs, W); lin(p + "mlp.shared.down", W, fs); lin(p + "mlp.shared.sg", 1, W, 2.0)
     return w

@@ -512,6 +512,56 @@ def bench_gatuzen(args):
     emit(out)
 
 
+# ------------------------------------------------------------------------------------------------- --arch lupolorn
+# width, layers (attention, minGRU, latent attention, attention in turn; dense feed-forward on the even layers, routed experts + a shared expert on the odd
+# ones), heads / kv heads / head size, dense ff, experts / top / expert ff, latent ranks, window
+LUPOLORN_SIZES = {
+    "s": dict(width=1024, n_layers=8, heads=8, kv_heads=2, head_dim=128, ff=4096, experts=8, top=2, expert_ff=1024, kv_rank=256, q_rank=512, window=1024, vocab=32000),
+    "m": dict(width=2048, n_layers=8, heads=16, kv_heads=4, head_dim=128, ff=8192, experts=16, top=2, expert_ff=2048, kv_rank=512, q_rank=1024, window=1024, vocab=32000),
+    "l": dict(width=4096, n_layers=8, heads=32, kv_heads=8, head_dim=128, ff=12288, experts=32, top=4, expert_ff=2048, kv_rank=512, q_rank=1536, window=2048, vocab=32000),
+}
+
+
+def bench_lupolorn(args):
+    """Prefill (one 2048-token prompt portion) and decode (1 and 8 sequences at context 2048) of a Lupolorn model with random weights, timed on
+    the device through the engine's own step, with the time of every kernel family against its roofline; beside it the engine's closest
+    design, Gatuzen (latent attention, recurrences, experts, the same layer frame), with the same width, layer count, heads, head size and experts."""
+    from aha_b200 import B200Model, synth
+    hbm, hbm_src = measured_peaks()
+    try:
+        tf = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        tf = 1590.0
+    K, W = max(args.steps if args.steps != 128 else 16, 4), max(args.warmup, 3)
+    out = {"metric": "Lupolorn prefill / decode tokens/s beside Gatuzen at equal size", "unit": UNIT, "data": "synthetic", "dtype": "bf16 weights, fp32 accumulate",
+           "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": hbm_src}, "prompt_tokens": 2048, "decode_ctx": 2048, "sizes": {}}
+    sampler = ClockSampler(0)
+    sampler.start()
+    for name in args.sizes.split(","):
+        sz = LUPOLORN_SIZES[name]
+        cfg = synth.lupolorn_shape(**sz)
+        log(f"[lupolorn {name}] weights ...")
+        w = synth.make_lupolorn(cfg, 0, fast=True)
+        m = B200Model("lupolorn", cfg, w, max_ctx=8 * 4096, max_prefill=2048, max_seqs=8)
+        del w
+        rec = {"config": sz, "weight_bytes": m.stats()["weight_bytes"]}
+        rec.update(_profile_layered(m, "lupolorn " + name, hbm, tf, W, K))
+        m.close()
+        gc = synth.gatuzen_shape(width=sz["width"], n_layers=sz["n_layers"], heads=sz["heads"], head_dim=sz["head_dim"], ff=sz["expert_ff"], experts=sz["experts"], top=sz["top"],
+                                 state=min(128, sz["head_dim"]), kv_rank=sz["kv_rank"], rot_dim=64, vocab=sz["vocab"])
+        log(f"[gatuzen {name}] weights ...")
+        gw = synth.make_gatuzen(gc, 0, fast=True)
+        gm = B200Model("gatuzen", gc, gw, max_ctx=8 * 4096, max_prefill=2048, max_seqs=8)
+        del gw
+        grec = {"weight_bytes": gm.stats()["weight_bytes"]}
+        grec.update(_profile_layered(gm, "gatuzen " + name, hbm, tf, W, K))
+        gm.close()
+        rec["gatuzen_equal_size"] = grec
+        out["sizes"][name] = rec
+    out["clocks"] = sampler.stop()
+    emit(out)
+
+
 def main():
     global _REAL_STDOUT
     sys.stdout.flush()
@@ -526,14 +576,16 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-tp", action="store_true", help="N > 1: skip the tensor-parallel (strong scaling) arm")
     ap.add_argument("--decode-impl", type=int, default=int(os.environ.get("AHA_DECODE_IMPL", "0")))
-    ap.add_argument("--arch", default="", help="'malasun' / 'gatuzen': throughput of the layered engine's Malasun design at model-like sizes beside Qwen3 at equal "
-                                               "width / depth (a separate report; the default workload and its JSON line are unchanged)")
-    ap.add_argument("--sizes", default="s,m", help="--arch malasun / gatuzen: which of the sizes s, m, l to run")
+    ap.add_argument("--arch", default="", help="'malasun' / 'gatuzen' / 'lupolorn': throughput of that design of the layered engine at model-like sizes beside its "
+                                               "closest relative at equal size (a separate report; the default workload and its JSON line are unchanged)")
+    ap.add_argument("--sizes", default="s,m", help="--arch malasun / gatuzen / lupolorn: which of the sizes s, m, l to run")
     args = ap.parse_args()
     if args.arch == "malasun":
         return bench_malasun(args)
     if args.arch == "gatuzen":      # the same kind of report for the Gatuzen design, beside Malasun at equal size
         return bench_gatuzen(args)
+    if args.arch == "lupolorn":     # ... and for the Lupolorn design, beside Gatuzen at equal size
+        return bench_lupolorn(args)
     K, W = args.steps, max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

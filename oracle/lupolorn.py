@@ -25,7 +25,7 @@ F = np.float64
 
 
 def sigmoid(z):
-    return 1.0 / (1.0 + np.exp(-z))
+    return 0.5 * (1.0 + np.tanh(0.5 * np.asarray(z, F)))
 
 
 def silu(z):
