@@ -63,8 +63,8 @@ inline void router_topk(cudaStream_t st, const RouterArgs& a) {
     AHA_CUDA_CHECK(cudaGetLastError());
 }
 
-// The router product, the softmax and the choice in ONE launch: a block owns TOK tokens, keeps their rows in shared memory, a warp forms one
-// output (an expert's logit, or the shared gate's) for all of them at a time from a single pass over that weight row, then warp r ranks token r.
+// The router product, the softmax and the choice in ONE launch: a block owns TOK tokens and keeps their rows in shared memory; its threads walk
+// every weight row together (a few rows at a time), the warps' partial sums meet in shared memory, then warp r ranks token r.
 // A token's sums run in an order that depends on K only, so its logits are the same whatever else is in the batch and whatever TOK is.
 struct RouterFusedArgs {
     const float* x; int ldx;         // [T, K] what the router reads
@@ -76,9 +76,11 @@ struct RouterFusedArgs {
 
 template <int TOK>
 static __global__ void __launch_bounds__(256) router_fused_kernel(RouterFusedArgs a) {
+    constexpr int EU = TOK == 1 ? 8 : 4;             // weight rows whose loads are in flight together
     extern __shared__ __align__(16) float rf_sm[];
     float* xs = rf_sm;                               // [TOK][K]
     float* lg = rf_sm + (size_t)TOK * a.K;           // [TOK][n_out]
+    float* part = lg + (size_t)TOK * a.n_out;        // [8 warps][n_out][TOK]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, t0 = blockIdx.x * TOK, nt = min(TOK, a.T - t0);
     const bool vec = (a.K & 3) == 0 && (a.ldx & 3) == 0;
     for (int r = 0; r < TOK; ++r) {
@@ -89,33 +91,56 @@ static __global__ void __launch_bounds__(256) router_fused_kernel(RouterFusedArg
         } else for (int k = tid; k < a.K; k += 256) xs[(size_t)r * a.K + k] = 0.f;
     }
     __syncthreads();
-    for (int e = warp; e < a.n_out; e += 8) {
-        const float* wr = a.w + (size_t)e * a.K;
-        float acc[TOK];
+    // the block's threads share every weight row (a thread takes every 256th piece of it) and EU rows at a time, so that a single block
+    // -- a decode step has no more than one per token -- still has most of the matrix requested at once
+    for (int e0 = 0; e0 < a.n_out; e0 += EU) {
+        float acc[EU][TOK];
 #pragma unroll
-        for (int r = 0; r < TOK; ++r) acc[r] = 0.f;
+        for (int u = 0; u < EU; ++u)
+#pragma unroll
+            for (int r = 0; r < TOK; ++r) acc[u][r] = 0.f;
         if (vec) {
-#pragma unroll(TOK == 1 ? 8 : 4)      // a row is a few kilobytes: most of its loads are in flight together
-            for (int k = lane * 4; k < a.K; k += 128) {
-                const float4 w4 = *reinterpret_cast<const float4*>(wr + k);
+#pragma unroll 2
+            for (int k = tid * 4; k < a.K; k += 1024) {
+                float4 w4[EU];
+#pragma unroll
+                for (int u = 0; u < EU; ++u) w4[u] = *reinterpret_cast<const float4*>(a.w + (size_t)min(e0 + u, a.n_out - 1) * a.K + k);
 #pragma unroll
                 for (int r = 0; r < TOK; ++r) {
                     const float4 x4 = *reinterpret_cast<const float4*>(xs + (size_t)r * a.K + k);
-                    acc[r] = fmaf(x4.w, w4.w, fmaf(x4.z, w4.z, fmaf(x4.y, w4.y, fmaf(x4.x, w4.x, acc[r]))));
+#pragma unroll
+                    for (int u = 0; u < EU; ++u) acc[u][r] = fmaf(x4.w, w4[u].w, fmaf(x4.z, w4[u].z, fmaf(x4.y, w4[u].y, fmaf(x4.x, w4[u].x, acc[u][r]))));
                 }
             }
         } else {
-            for (int k = lane; k < a.K; k += 32) {
-                const float wv = wr[k];
+            for (int k = tid; k < a.K; k += 256) {
+                float wv[EU];
 #pragma unroll
-                for (int r = 0; r < TOK; ++r) acc[r] = fmaf(xs[(size_t)r * a.K + k], wv, acc[r]);
+                for (int u = 0; u < EU; ++u) wv[u] = a.w[(size_t)min(e0 + u, a.n_out - 1) * a.K + k];
+#pragma unroll
+                for (int r = 0; r < TOK; ++r) {
+                    const float xv = xs[(size_t)r * a.K + k];
+#pragma unroll
+                    for (int u = 0; u < EU; ++u) acc[u][r] = fmaf(xv, wv[u], acc[u][r]);
+                }
             }
         }
 #pragma unroll
-        for (int r = 0; r < TOK; ++r) {
-            const float v = warp_sum(acc[r]);
-            if (lane == 0 && r < nt) { lg[r * a.n_out + e] = v; a.logits[(size_t)(t0 + r) * a.ld + e] = v; }
-        }
+        for (int u = 0; u < EU; ++u)
+#pragma unroll
+            for (int r = 0; r < TOK; ++r) {
+                const float v = warp_sum(acc[u][r]);
+                if (lane == 0 && e0 + u < a.n_out) part[((size_t)warp * a.n_out + e0 + u) * TOK + r] = v;
+            }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < a.n_out * TOK; idx += 256) {      // the warps' parts in a fixed order
+        const int e = idx / TOK, r = idx % TOK;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v += part[((size_t)w * a.n_out + e) * TOK + r];
+        lg[r * a.n_out + e] = v;
+        if (r < nt) a.logits[(size_t)(t0 + r) * a.ld + e] = v;
     }
     __syncthreads();
     for (int r = warp; r < nt; r += 8) {
@@ -149,7 +174,7 @@ static __global__ void __launch_bounds__(256) router_fused_kernel(RouterFusedArg
     }
 }
 
-inline size_t router_fused_smem(int tok, int K, int n_out) { return (size_t)tok * (K + n_out) * sizeof(float); }
+inline size_t router_fused_smem(int tok, int K, int n_out) { return (size_t)tok * (K + 9 * n_out) * sizeof(float); }
 inline bool router_fused_supported(int K, int n_out) { return router_fused_smem(8, K, n_out) <= 200 * 1024; }
 
 // decode-sized steps give every token a block of its own (the weight rows are then read once per token, which a few tokens can afford)
