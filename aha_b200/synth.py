@@ -581,7 +581,7 @@ def lupolorn_shape(width, n_layers, heads, kv_heads, head_dim, ff, experts, top,
             layers.append({"type": "latent_attention", "heads": heads, "dim": head_dim, "vdim": head_dim, "kv_rank": kv_rank, "q_rank": q_rank, "window": window, "ff": f})
         else:
             layers.append({"type": "attention", "heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "rot_dims": head_dim, "base": 5e5,
-                           "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}, "ff": f})
+                           "scaling": {"factor": 4.0, "low": 1.0, "high": 2.0, "original": 8192}, "ff": f})
     return lupolorn_config(layers, width=width, vocab=vocab, eps=1e-6, embed_scale=float(np.sqrt(width)))
 
 

@@ -471,3 +471,39 @@ def test_sampler_runs_on_the_engine():
     b, _ = p.m.generate(pr, max_tokens=8, temperature=0.8, top_p=0.9, top_k=20, seed=5)
     assert a == b and len(a) == 8 and all(0 <= t < cfg["vocab"] for t in a)
     p.close()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_shapes_that_tile_for_the_tensor_cores(seed):
+    # widths, head sizes and feed-forward sizes that the tcgen05 kernels take (multiples of 64; head size 64 / 128), everything else drawn at random:
+    # group counts, windows that end inside a tile, expert counts, layer order; serving mode and exact mode must both agree with the plain implementation
+    r = np.random.default_rng(300 + seed)
+    pick = lambda *xs: xs[int(r.integers(0, len(xs)))]
+    width = pick(64, 128, 192, 320)
+
+    def ff():
+        n = pick(2, 3, 6)
+        return pick(None, pick(64, 192), E(n, int(r.integers(1, n + 1)), pick(64, 128), pick(None, 64, 96)))
+
+    def layer():
+        t = pick("mingru", "attention", "latent")
+        if t == "mingru":
+            return R(width=pick(64, 96, 160), ff=ff())
+        if t == "attention":
+            g, d = pick(1, 2, 3), pick(64, 128)
+            sc = pick(None, {"factor": pick(2.0, 16.0), "low": pick(1.0, 2.0), "high": pick(4.0, 8.0), "original": pick(32, 128)})
+            return A(heads=g * pick(1, 2, 3), kv_heads=g, dim=d, vdim=d, rot_dims=pick(d, d // 2, 2), base=pick(1e3, 1e6), scaling=sc, scale=pick(None, 0.1), ff=ff())
+        dv = pick(64, 128)
+        return Lt(heads=pick(1, 2, 5), dim=pick(32, 64, 128), vdim=dv, kv_rank=pick(32, 64, 80), q_rank=pick(24, 64, 128), window=pick(1, 33, 64, 150, 257, 1000), scale=pick(None, 0.1), ff=ff())
+
+    layers = [layer() for _ in range(int(r.integers(2, 5)))]
+    cfg = synth.lupolorn_config(layers, width=width, vocab=pick(64, 100, 160), eps=pick(1e-6, 1e-5), embed_scale=pick(1.0, 8.0))
+    exact = seed % 2 == 1
+    p = Pair(cfg, seed=seed, exact=exact, max_ctx=1024, max_seqs=3, step_tokens=pick(256, 1024))
+    ids = p.ids(600, seed)
+    want = p.o.forward(ids)
+    for cuts in ([], [33, 35, 100, 164, 300, 333, 560] + list(range(580, 600))):
+        got = p.run_cuts(ids, cuts)
+        err = np.abs(got - want).max() / max(1.0, want.std())
+        assert err < (TOL32 if exact else 3e-3), (cuts[:3], err, int(np.abs(got - want).max(axis=1).argmax()))
+    p.close()
