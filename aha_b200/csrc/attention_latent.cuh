@@ -6,7 +6,8 @@
 // per-head products are batched matrix products (gemm_any.cuh), the attention itself is the ragged kernel of attention_window.cuh.
 //
 //   latent_prep_kernel   per token: RMS norm of the latent (gain per channel) and rotary embedding of the shared key part into the page
-//                        of the token's position; rotary embedding of every head's rotated query part into the absorbed-query buffer.
+//                        of the token's position; rotary embedding of every head's rotated query part into the absorbed-query buffer;
+//                        optionally the RMS norm of a query latent in place (queries that are expanded from a latent of their own).
 // Rotary: interleaved pairs (2i, 2i + 1) of the first 2 * n_freq coordinates turn by pos * freq[i]; cos and sin carry `mult` (YaRN's
 // attention factor); further coordinates pass unchanged.  Angles are fp32 products, cos / sin the accurate functions.
 #pragma once
@@ -50,6 +51,8 @@ struct LatentPrepArgs {
     float* q_abs; int ld_q;         // [T, H * (rank + R)]: the rotated query part goes to columns h * (rank + R) + rank ...
     PagedKV kv;                     // G = 1, D = rank + R
     RaggedBatch rb;
+    // a query latent that is normed on the way (in place, gain per channel): columns ql_off .. ql_off + ql_rank - 1 of the projected rows; 0: none
+    int ql_off = 0, ql_rank = 0; const float* ql_norm = nullptr;
 };
 
 static __global__ void latent_prep_kernel(LatentPrepArgs a) {
@@ -65,6 +68,14 @@ static __global__ void latent_prep_kernel(LatentPrepArgs a) {
     ss = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)a.rank + a.eps);
     for (int i = threadIdx.x; i < a.rank; i += blockDim.x) krow[i] = d[i] * inv * a.c_norm[i];
+    if (a.ql_rank > 0) {
+        float* ql = a.proj + (size_t)t * a.ld + a.ql_off;
+        float sq = 0.f;
+        for (int i = threadIdx.x; i < a.ql_rank; i += blockDim.x) sq = fmaf(ql[i], ql[i], sq);
+        sq = block_sum(sq, red);
+        const float iq = 1.0f / sqrtf(sq / (float)a.ql_rank + a.eps);
+        for (int i = threadIdx.x; i < a.ql_rank; i += blockDim.x) ql[i] = ql[i] * iq * a.ql_norm[i];
+    }
     // rotated parts: item (0, pair) is the shared key part, item (1 + h, pair) head h's query part; pairs beyond n_freq are single pass-through coordinates
     const int half = a.n_freq, rest = a.R - 2 * half, per = half + rest;
     const float fpos = (float)pos;

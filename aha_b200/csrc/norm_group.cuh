@@ -108,6 +108,65 @@ static __global__ void post_pre_norm_kernel(PostPreNormArgs a) {
     for (int c = threadIdx.x; c < a.C; c += blockDim.x) h[c] = x[c] * sc2 * a.w_pre[c];
 }
 
+// The same with a row's values in registers (C % 4 == 0, C <= 4 NV blockDim): y and x are read once, 16 bytes at a time.
+template <int NV>
+static __global__ void post_pre_norm_reg_kernel(PostPreNormArgs a) {
+    __shared__ float red[32];
+    const size_t r = blockIdx.x;
+    const int C4 = a.C >> 2;
+    const float4* __restrict__ y4 = reinterpret_cast<const float4*>(a.y + r * a.C);
+    float4* x4 = reinterpret_cast<float4*>(a.x + r * a.C);
+    float4 yv[NV], xv[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        yv[i] = c < C4 ? y4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        xv[i] = c < C4 ? x4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) ss = fmaf(yv[i].x, yv[i].x, fmaf(yv[i].y, yv[i].y, fmaf(yv[i].z, yv[i].z, fmaf(yv[i].w, yv[i].w, ss))));
+    ss = block_sum(ss, red);
+    const float sc = a.mult / sqrtf(ss / (float)a.C + a.eps);
+    float s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < C4) {
+            const float4 w = reinterpret_cast<const float4*>(a.w_post)[c];
+            xv[i].x += yv[i].x * sc * w.x; xv[i].y += yv[i].y * sc * w.y; xv[i].z += yv[i].z * sc * w.z; xv[i].w += yv[i].w * sc * w.w;
+            x4[c] = xv[i];
+            s2 = fmaf(xv[i].x, xv[i].x, fmaf(xv[i].y, xv[i].y, fmaf(xv[i].z, xv[i].z, fmaf(xv[i].w, xv[i].w, s2))));
+        }
+    }
+    s2 = block_sum(s2, red);
+    const float sc2 = 1.0f / sqrtf(s2 / (float)a.C + a.eps);
+    float4* h4 = reinterpret_cast<float4*>(a.h + r * a.C);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < C4) {
+            const float4 w = reinterpret_cast<const float4*>(a.w_pre)[c];
+            h4[c] = make_float4(xv[i].x * sc2 * w.x, xv[i].y * sc2 * w.y, xv[i].z * sc2 * w.z, xv[i].w * sc2 * w.w);
+        }
+    }
+}
+
+// rows <= 8 (a decode step has few blocks): more threads for each
+inline void post_pre_norm(cudaStream_t st, const PostPreNormArgs& a, int rows) {
+    if (rows == 0) return;
+    const int threads = rows <= 8 ? std::min(1024, std::max(128, (a.C / 4 + 31) / 32 * 32)) : 256;
+    const int nv = (a.C / 4 + threads - 1) / threads;
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (a.C % 4 == 0 && nv <= 8 && al(a.y) && al(a.x) && al(a.h) && al(a.w_post) && al(a.w_pre)) {
+        if (nv <= 1) post_pre_norm_reg_kernel<1><<<rows, threads, 0, st>>>(a);
+        else if (nv <= 2) post_pre_norm_reg_kernel<2><<<rows, threads, 0, st>>>(a);
+        else if (nv <= 4) post_pre_norm_reg_kernel<4><<<rows, threads, 0, st>>>(a);
+        else post_pre_norm_reg_kernel<8><<<rows, threads, 0, st>>>(a);
+    } else post_pre_norm_kernel<<<rows, threads, 0, st>>>(a);
+    AHA_CUDA_CHECK(cudaGetLastError());
+}
+
 constexpr int kShortConvMaxTaps = 16;
 
 struct ShortConvArgs {

@@ -644,7 +644,7 @@ struct Engine final : SeqEngine {
             tic("norm + residual + next norm", 8.0 * T * W, 20.0 * T * W);
             PostPreNormArgs a{};
             a.y = y; a.x = x; a.w_post = gain; a.w_pre = next_pre; a.h = hnorm; a.eps = eps; a.mult = resid_mult; a.C = W;
-            post_pre_norm_kernel<<<T, T <= 8 ? std::min(1024, std::max(128, (W / 2 + 31) / 32 * 32)) : 256, 0, c.stream>>>(a);
+            post_pre_norm(c.stream, a, T);
             c.cnt.kernels++;
             pre_ready = next_pre;
             toc();
@@ -1176,7 +1176,10 @@ struct LatentAttentionMixer final : Sublayer {
         const int T = v.rb.T, ldq = H * (rank + R);
         cudaStream_t st = E.c.stream;
         E.gemm(AEPI_STORE, v.x, E.W, in, E.proj, ld, T);
-        if (q_rank > 0) {      // q = W_uq norm(W_dq h): the latent is normed in place, the queries land behind the stacked projection
+        // q = W_uq norm(W_dq h): the query latent is normed in place and the queries land behind the stacked projection.  Without a rotated part
+        // the prep kernel has nothing to do on the queries themselves, so it runs first and norms the query latent on the way.
+        const bool norm_in_prep = q_rank > 0 && R == 0;
+        if (q_rank > 0 && !norm_in_prep) {
             E.tic("query latent norm", 4.0 * T * q_rank, 8.0 * T * q_rank);
             GroupNormArgs n{};
             n.in = E.proj; n.ld_in = ld; n.w = q_norm; n.eps = E.eps; n.C = q_rank; n.groups = 1; n.out = E.proj; n.ld_out = ld;
@@ -1184,14 +1187,16 @@ struct LatentAttentionMixer final : Sublayer {
             E.toc();
             E.gemm(AEPI_STORE, E.proj, ld, uq, E.proj + q_off, ld, T);
         }
-        E.tic("latent norm + rotary + cache write", 8.0 * T * (rank + (H + 1) * R), 8.0 * T * (rank + (H + 1) * R));
+        E.tic("latent norm + rotary + cache write", 8.0 * T * (rank + q_rank + (H + 1) * R), 8.0 * T * (rank + q_rank + (H + 1) * R));
         LatentPrepArgs a{};
         a.proj = E.proj; a.ld = ld; a.q_off = q_off; a.dkv_off = dkv_off; a.H = H; a.D = D; a.R = R; a.rank = rank; a.c_norm = c_norm; a.eps = E.eps;
         a.freq = freq; a.n_freq = n_freq; a.mult = rot_mult; a.q_abs = E.qbuf; a.ld_q = ldq; a.kv = kv; a.rb = v.rb;
+        if (norm_in_prep) { a.ql_off = 0; a.ql_rank = q_rank; a.ql_norm = q_norm; }
         latent_prep_kernel<<<T, T <= 8 ? 512 : 128, 0, st>>>(a);
         E.c.cnt.kernels++;
         AHA_CUDA_CHECK(cudaGetLastError());
         E.toc();
+        if (norm_in_prep) E.gemm(AEPI_STORE, E.proj, ld, uq, E.proj + q_off, ld, T);
         // which entries are prompt portions (expanded keys / values, below) and which are served by the absorbed form
         bool any_long = false, all_long = can_expand;
         for (int e = 0; e < v.rb.E; ++e) {
