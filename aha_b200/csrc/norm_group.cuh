@@ -85,6 +85,11 @@ struct PostPreNormArgs {
     float* h;                  // [T, C] what the next sublayer reads
     float eps, mult;
     int C;
+    // (register kernel only) y formed on the way from a token's expert rows: y[t] = sum_k mix_w[t][k] * mix_rows[t * mix_top + k] (+ sigmoid(mix_gate[t]) *
+    // mix_shared[t]) -- the combine step of routed experts in decode steps, in the order the combine kernel sums
+    const float* mix_rows = nullptr; int mix_top = 0;
+    const float* mix_w = nullptr; int mix_ldw = 0;
+    const float* mix_shared = nullptr; const float* mix_gate = nullptr; int mix_ldg = 0;
 };
 
 static __global__ void post_pre_norm_kernel(PostPreNormArgs a) {
@@ -121,8 +126,24 @@ static __global__ void post_pre_norm_reg_kernel(PostPreNormArgs a) {
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
-        yv[i] = c < C4 ? y4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
         xv[i] = c < C4 ? x4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!a.mix_rows) yv[i] = c < C4 ? y4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        else {
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < C4) {
+                for (int k = 0; k < a.mix_top; ++k) {
+                    const float w = a.mix_w[r * a.mix_ldw + k];
+                    const float4 v = reinterpret_cast<const float4*>(a.mix_rows + (r * a.mix_top + k) * a.C)[c];
+                    s.x = fmaf(w, v.x, s.x); s.y = fmaf(w, v.y, s.y); s.z = fmaf(w, v.z, s.z); s.w = fmaf(w, v.w, s.w);
+                }
+                if (a.mix_shared) {
+                    const float g = sigmoid_f(a.mix_gate[r * a.mix_ldg]);
+                    const float4 v = reinterpret_cast<const float4*>(a.mix_shared + r * a.C)[c];
+                    s.x = fmaf(g, v.x, s.x); s.y = fmaf(g, v.y, s.y); s.z = fmaf(g, v.z, s.z); s.w = fmaf(g, v.w, s.w);
+                }
+            }
+            yv[i] = s;
+        }
     }
 #pragma unroll
     for (int i = 0; i < NV; ++i) ss = fmaf(yv[i].x, yv[i].x, fmaf(yv[i].y, yv[i].y, fmaf(yv[i].z, yv[i].z, fmaf(yv[i].w, yv[i].w, ss))));
@@ -152,13 +173,18 @@ static __global__ void post_pre_norm_reg_kernel(PostPreNormArgs a) {
     }
 }
 
-// rows <= 8 (a decode step has few blocks): more threads for each
+inline int post_pre_norm_threads(int C, int rows) { return rows <= 8 ? std::min(1024, std::max(128, (C / 4 + 31) / 32 * 32)) : 256; }      // a decode step has few blocks: more threads for each
+// whether the register kernel (the only one that forms y from expert rows) takes this row size; the engine's buffers are 16-byte aligned
+inline bool post_pre_norm_in_registers(int C, int rows) { return C % 4 == 0 && (C / 4 + post_pre_norm_threads(C, rows) - 1) / post_pre_norm_threads(C, rows) <= 8; }
+
 inline void post_pre_norm(cudaStream_t st, const PostPreNormArgs& a, int rows) {
     if (rows == 0) return;
-    const int threads = rows <= 8 ? std::min(1024, std::max(128, (a.C / 4 + 31) / 32 * 32)) : 256;
+    const int threads = post_pre_norm_threads(a.C, rows);
     const int nv = (a.C / 4 + threads - 1) / threads;
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-    if (a.C % 4 == 0 && nv <= 8 && al(a.y) && al(a.x) && al(a.h) && al(a.w_post) && al(a.w_pre)) {
+    const bool reg = post_pre_norm_in_registers(a.C, rows) && al(a.y) && al(a.x) && al(a.h) && al(a.w_post) && al(a.w_pre) && al(a.mix_rows) && al(a.mix_shared);
+    AHA_REQUIRE(reg || !a.mix_rows, "post_pre_norm: expert rows are summed by the register kernel only");
+    if (reg) {
         if (nv <= 1) post_pre_norm_reg_kernel<1><<<rows, threads, 0, st>>>(a);
         else if (nv <= 2) post_pre_norm_reg_kernel<2><<<rows, threads, 0, st>>>(a);
         else if (nv <= 4) post_pre_norm_reg_kernel<4><<<rows, threads, 0, st>>>(a);

@@ -529,7 +529,7 @@ struct Engine final : SeqEngine {
                      float* logits_out, const std::vector<size_t>* want_out) {
         cudaStream_t st = c.stream;
         const int T = rb.T;
-        pre_ready = nullptr;
+        pre_ready = nullptr; mix_pending = false;
         if (any_fb) { feedback_tokens_kernel<<<ceil_div(T, 256), 256, 0, st>>>(reinterpret_cast<uint32_t*>(d_meta), d_fb, d_states, T); c.cnt.kernels++; }
         if (fp32) embed_gather_any_kernel<float><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const float*>(embed), x, W, V, embed_scale);
         else embed_gather_any_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const __nv_bfloat16*>(embed), x, W, V, embed_scale);
@@ -639,11 +639,24 @@ struct Engine final : SeqEngine {
     }
     // ... and what it leaves: x += m * group norm(y) * gain
     const float* pre_ready = nullptr;      // the gain of the pre-norm whose result hnorm already holds
+    // routed experts of a decode-sized step may leave their weighted sum to the launch that follows (see PostPreNormArgs::mix_*)
+    WeightedCombineArgs mix{}; bool mix_pending = false;
+    bool can_defer_mix(int T) const { return sandwich && norm_groups == 1 && post_pre_norm_in_registers(W, T); }
     void sublayer_output(int T, const float* gain, const float* next_pre = nullptr) {
-        if (next_pre && norm_groups == 1 && !out_src) {
+        const bool fuse = next_pre && norm_groups == 1 && !out_src;
+        if (mix_pending && !fuse) {          // nothing to ride with (the last sublayer of the model): the combine kernel after all
+            moe_weighted_combine_kernel<<<(unsigned)((mix.total + 255) / 256), 256, 0, c.stream>>>(mix);
+            c.cnt.kernels++;
+            mix_pending = false;
+        }
+        if (fuse) {
             tic("norm + residual + next norm", 8.0 * T * W, 20.0 * T * W);
             PostPreNormArgs a{};
             a.y = y; a.x = x; a.w_post = gain; a.w_pre = next_pre; a.h = hnorm; a.eps = eps; a.mult = resid_mult; a.C = W;
+            if (mix_pending) {
+                a.mix_rows = mix.rows; a.mix_top = mix.top; a.mix_w = mix.weights; a.mix_ldw = mix.ld_w; a.mix_shared = mix.shared; a.mix_gate = mix.gate; a.mix_ldg = mix.ld_gate;
+                mix_pending = false;
+            }
             post_pre_norm(c.stream, a, T);
             c.cnt.kernels++;
             pre_ready = next_pre;
@@ -1528,10 +1541,11 @@ struct RoutedMoeFF final : Sublayer {
             E.gemm(act, v.x, W, sup, shid, ffs, T);
             E.gemm(AEPI_STORE, shid, ffs, sdown, sout, W, T);
         }
-        E.tic("expert combine", 2.0 * (A + T) * W, 4.0 * (A + 2.0 * T) * W);
         WeightedCombineArgs cb{};
         cb.rows = rows_out; cb.place_of = rows ? nullptr : place_of; cb.weights = logits + n_router; cb.ld_w = ldl;
         cb.shared = ffs > 0 ? sout : nullptr; cb.gate = logits + experts; cb.ld_gate = ldl; cb.y = v.y; cb.C = W; cb.top = top; cb.total = (size_t)T * W;
+        if (rows && E.can_defer_mix(T)) { E.mix = cb; E.mix_pending = true; return; }      // summed by the norm + residual launch that follows
+        E.tic("expert combine", 2.0 * (A + T) * W, 4.0 * (A + 2.0 * T) * W);
         moe_weighted_combine_kernel<<<(unsigned)((cb.total + 255) / 256), 256, 0, st>>>(cb);
         E.c.cnt.kernels++;
         AHA_CUDA_CHECK(cudaGetLastError());
