@@ -59,7 +59,7 @@ def write_safetensors(path, tensors):
 def model_kind(config):
     """Which executor a config.json asks for."""
     arch = config.get("architecture")
-    if isinstance(arch, str) and arch.lower() in ("malasun", "gatuzen", "lupolorn"):      # designs of the layered engine: config.json lists the layers
+    if isinstance(arch, str) and arch.lower() in ("malasun", "gatuzen", "lupolorn", "gomerax"):      # designs of the layered engine: config.json lists the layers
         return arch.lower()
     names = " ".join(config.get("architectures", []) + [config.get("model_type", "")]).lower()
     if "qwen3_asr" in names or "qwen3asr" in names or "thinker_config" in config:

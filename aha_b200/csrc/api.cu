@@ -567,7 +567,7 @@ int aha_b200_create(const char* kind, const char* config_json, const aha_tensor_
             m->text.load(m->ctx, tc, wt, "thinker.model.", "thinker.lm_head.weight", tp_rank, tp_world);
             m->audio.load(m->ctx, AudioCfg::from_json(tk.at("audio_config")), wt, "thinker.audio_tower.", o.max_frames > 0 ? o.max_frames : 3000);
             AHA_REQUIRE(m->audio.cfg.out_dim == tc.H, "audio output_dim must equal the text hidden_size");
-        } else if (k == "malasun" || k == "gatuzen" || k == "lupolorn" || k == "layered") {
+        } else if (k == "malasun" || k == "gatuzen" || k == "lupolorn" || k == "gomerax" || k == "layered") {
             // a model that is a list of layers (config.json "layers"); reserved[1] = 1: exact fp32 mode, reserved[2]: sequence slots (0 = 8)
             AHA_REQUIRE(tp_world == 1, "the layered engine is single-GPU");
             m->kind = aha_model::LAYERED;
@@ -581,7 +581,7 @@ int aha_b200_create(const char* kind, const char* config_json, const aha_tensor_
             so.seq_impl = o.reserved[0] == 1 ? 1 : 0;     // attn_impl 1: the plain sequence kernels
             m->seq.reset(make_layered_engine(m->ctx, root, wt, so));
         } else {
-            throw std::runtime_error("unknown model kind '" + k + "' (expected qwen3 | qwen3vl | qwen3_asr | malasun | gatuzen | lupolorn)");
+            throw std::runtime_error("unknown model kind '" + k + "' (expected qwen3 | qwen3vl | qwen3_asr | malasun | gatuzen | lupolorn | gomerax)");
         }
         if (m->kind == aha_model::LAYERED) {
             for (size_t i = 0; i < n_eos; ++i) m->stop_ids.push_back(eos_ids[i]);

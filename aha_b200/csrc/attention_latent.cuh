@@ -132,6 +132,7 @@ struct LatentFlashArgs {
     int D, R, Dv;
     float scale;
     int window = 0;                                        // > 0: query i sees keys j with 0 <= i - j < window
+    const float* sink = nullptr;                           // [H]: the softmax denominator of head h also holds exp(sink[h]) (no key, no value, not scaled)
 };
 
 constexpr int kLfBQ = 64, kLfBK = 64, kLfThreads = 256;
@@ -303,7 +304,11 @@ static __global__ void __launch_bounds__(kLfThreads) latent_flash_kernel(LatentF
     for (int i = 0; i < 4; ++i) {
         const int r = 4 * ty + i;
         if (r >= nq) continue;
-        const float inv = 1.0f / l[i];
+        float inv = 1.0f / l[i];
+        if (a.sink) {                  // bring the sums to max(m, sink), the maximum once the sink takes part
+            const float sk = a.sink[h], M = fmaxf(m[i], sk), w = expf(m[i] - M);
+            inv = w / (l[i] * w + expf(sk - M));
+        }
         float* orow = a.out + (size_t)(a.t0 + q0 + r) * a.ld_o + (size_t)h * a.Dv;
 #pragma unroll
         for (int j = 0; j < NV; ++j)

@@ -98,17 +98,18 @@ inline void latent_flash_tc_launch(cudaStream_t st, const LatentFlashArgs& a, in
     FlashTcArgs m;
     m.out = a.out; m.o_tok_stride = (size_t)a.ld_o; m.o_head_stride = (size_t)HD; m.out_hi = nullptr; m.out_lo = nullptr;
     m.Sq = a.n; m.Skv = S; m.q0 = a.t0; m.groups = 1; m.scaling = a.scale; m.window = a.window;
+    if (a.sink) { m.sink = 1; m.sink_logit = a.sink; }
     static bool attr = false;      // (the instances the library's start-up does not know)
     if (!attr) { AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<HD, true, WIN, HDQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)flash_tc_smem_bytes<HD, HDQ>())); attr = true; }
     flash_attn_tc_kernel<HD, true, WIN, HDQ><<<dim3(ceil_div(a.n, kFaBQ), H), kFaThreads, flash_tc_smem_bytes<HD, HDQ>(), st>>>(tqh, tql, tkh, tkl, tvh, tvl, m);
     AHA_CUDA_CHECK(cudaGetLastError());
 }
 
-// a: as for latent_flash (the entry's queries, the expanded keys / values of positions 0 .. S - 1).  A sliding window runs the kernel's
-// windowed instances.  Returns the launches.
+// a: as for latent_flash (the entry's queries, the expanded keys / values of positions 0 .. S - 1).  A sliding window or a sink runs the
+// kernel's windowed instances (window 0: every earlier key).  Returns the launches.
 inline int latent_flash_tc(cudaStream_t st, const LatentFlashArgs& a, int H, __half* ws) {
     const int S = a.pos0 + a.n, HDQ = latent_flash_tc_hdq(a.D, a.R, a.Dv);
-    if (a.window > 0) {
+    if (a.window > 0 || a.sink) {
         if (a.Dv == 128) { if (HDQ == 128) latent_flash_tc_launch<128, 128, true>(st, a, H, S, ws); else latent_flash_tc_launch<128, 192, true>(st, a, H, S, ws); }
         else { if (HDQ == 64) latent_flash_tc_launch<64, 64, true>(st, a, H, S, ws); else latent_flash_tc_launch<64, 128, true>(st, a, H, S, ws); }
         return 2;

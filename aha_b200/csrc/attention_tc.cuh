@@ -107,6 +107,7 @@ struct FlashTcArgs {
     size_t gate_tok_stride = 0;
     const float* gate_head = nullptr;   // ... or ONE gate number per head, read from gate_head[(q0 + i) * gate_tok_stride + head]
     int sink = 0;                       // 1: the softmax denominator holds an extra exp(0): a key of score 0 that has no value
+    const float* sink_logit = nullptr;  // [heads] with sink == 1: that key's score is this number of the head (not scaled) instead of 0
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {   // 2^x on the MUFU, flush-to-zero (inputs here are <= 0; -inf -> 0)
@@ -352,7 +353,8 @@ __global__ void __launch_bounds__(kFaThreads, (HD == 64 && HDQ == 64) ? 2 : 1) f
             tc_fence_before();
         }
         if (qi < a.Sq) {
-            if (WIN && a.sink) l += exp2f(-m);      // m is the row's maximum in the log2 domain: the score 0 weighs 2^(0 - m)
+            // m is the row's maximum in the log2 domain: a sink of score s weighs 2^(s log2(e) - m)
+            if (WIN && a.sink) l += exp2f((a.sink_logit ? a.sink_logit[head] * 1.4426950408889634f : 0.f) - m);
             float inv = 1.0f / l;
             if (WIN && a.gate_head) inv *= sigmoid_f(a.gate_head[(size_t)(a.q0 + qi) * a.gate_tok_stride + head]);
             const size_t off = (size_t)(a.q0 + qi) * a.o_tok_stride + (size_t)head * a.o_head_stride;
@@ -416,6 +418,7 @@ struct FlashWindow {        // what the WIN kernels add to causal attention; win
     size_t gate_tok_stride = 0;
     const float* gate_head = nullptr;   // one gate number per head instead of one per channel
     int sink = 0;
+    const float* sink_logit = nullptr;  // see FlashTcArgs
 };
 // head_dim 64 (ViT, audio encoder: 2 CTAs per SM) and 128 (LLM prefill, causal, GQA, paged KV: 1 CTA per SM).  `ws`: at least flash_tc_ws_halfs<HD>() halfs.
 template <int HD>
@@ -439,7 +442,7 @@ inline void flash_attn_tc(cudaStream_t st, const FlashArgs& a, int nheads, bool 
     const size_t smem = flash_tc_smem_bytes<HD>();
     if (win) {
         AHA_REQUIRE(causal, "windowed attention is causal");
-        m.window = win->window; m.slopes = win->slopes; m.gate = win->gate; m.gate_tok_stride = win->gate_tok_stride; m.gate_head = win->gate_head; m.sink = win->sink;
+        m.window = win->window; m.slopes = win->slopes; m.gate = win->gate; m.gate_tok_stride = win->gate_tok_stride; m.gate_head = win->gate_head; m.sink = win->sink; m.sink_logit = win->sink_logit;
         AHA_CUDA_CHECK(cudaFuncSetAttribute(flash_attn_tc_kernel<HD, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         flash_attn_tc_kernel<HD, true, true><<<grid, kFaThreads, smem, st>>>(tqh, tql, tkh, tkl, tvh, tvl, m);
     } else if (causal) flash_attn_tc_kernel<HD, true><<<grid, kFaThreads, smem, st>>>(tqh, tql, tkh, tkl, tvh, tvl, m);

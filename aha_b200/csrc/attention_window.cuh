@@ -225,6 +225,7 @@ struct WindowAttnArgs {
     const float* gate; int gate_ld;   // raw gate pre-activations [T, .] (column h*Dv + c) or nullptr
     int gate_per_head = 0;   // 1: the gate has ONE number per head (column h)
     int sink = 0;            // 1: one is added to the softmax denominator (a key of score 0 that has no value)
+    const float* sink_logit = nullptr;   // [H] with sink == 1: the extra key's score is this learned number of the head (unscaled) instead of 0
     float* out;              // [T, H*Dv]
     int H;
     RaggedBatch rb;
@@ -326,9 +327,10 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_kernel(Win
         return;
     }
     float inv = 1.0f / l;
-    if (a.sink) {                      // bring the sums to max(m, 0), the maximum once the score 0 takes part
-        const float M = fmaxf(m, 0.f), w = expf(m - M);
-        inv = w / (l * w + expf(-M));
+    if (a.sink) {                      // bring the sums to max(m, sink score), the maximum once the sink takes part
+        const float sk = a.sink_logit ? a.sink_logit[h] : 0.f;
+        const float M = fmaxf(m, sk), w = expf(m - M);
+        inv = w / (l * w + expf(sk - M));
     }
 #pragma unroll
     for (int r = 0; r < kWinAttnMaxAcc; ++r) {
@@ -352,9 +354,10 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_merge_kern
     const bool mine = tid < a.nsplit;
     const float ms = mine ? P[(size_t)tid * (2 + Dv)] : -INFINITY, ls = mine ? P[(size_t)tid * (2 + Dv) + 1] : 0.f;
     float M = block_max(ms, red);
-    if (a.sink) M = fmaxf(M, 0.f);
+    const float sk = a.sink && a.sink_logit ? a.sink_logit[h] : 0.f;
+    if (a.sink) M = fmaxf(M, sk);
     const float wgt = ls > 0.f ? expf(ms - M) : 0.f;
-    const float L = block_sum(ls * wgt, red) + (a.sink ? expf(-M) : 0.f);
+    const float L = block_sum(ls * wgt, red) + (a.sink ? expf(sk - M) : 0.f);
     if (mine) wsm[tid] = wgt / L;
     __syncthreads();
     float o[kWinAttnMaxAcc];          // channels tid, tid + 128, ...: their loads of a chunk are in flight together

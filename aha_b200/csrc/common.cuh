@@ -99,7 +99,15 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-
 
 __device__ __forceinline__ float relu2_f(float x) { const float r = fmaxf(x, 0.f); return r * r; }      // the square of relu
 
-enum Act { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_ERF = 2, ACT_GELU_TANH = 3, ACT_XIELU = 4 /* two parameters: callers use xielu_f */, ACT_RELU2 = 5 };
+// A gated unit with clamped inputs: the gate is cut off above `limit`, the other input clamped to [-limit, limit] and shifted by one;
+// the gate passes through g * sigmoid(slope * g).
+__device__ __forceinline__ float clamp_glu_f(float gate, float up, float limit, float slope) {
+    const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+    return g * sigmoid_f(slope * g) * (u + 1.f);
+}
+
+enum Act { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_ERF = 2, ACT_GELU_TANH = 3, ACT_XIELU = 4 /* two parameters: callers use xielu_f */, ACT_RELU2 = 5,
+           ACT_CLAMP_GLU = 6 /* a gated unit of two inputs and two parameters: callers use clamp_glu_f */ };
 __device__ __forceinline__ float apply_act(int act, float x) {
     switch (act) {
         case ACT_SILU: return silu_f(x);

@@ -12,7 +12,9 @@
 
 namespace aha {
 
-enum AnyEpi { AEPI_STORE = 0, AEPI_XIELU = 1, AEPI_SWIGLU = 2, AEPI_RELU2 = 3 };   // SWIGLU: rows of W alternate gate / up; C[m][n / 2] = silu(gate) * up (N even); RELU2: max(v, 0)^2
+// SWIGLU: rows of W alternate gate / up; C[m][n / 2] = silu(gate) * up (N even); RELU2: max(v, 0)^2; CLAMP_GLU: rows alternate as for SWIGLU,
+// the unit is clamp_glu_f(gate, up, act_a = limit, act_b = slope) (it runs the SWIGLU kernels with GemmAnyArgs::glu set)
+enum AnyEpi { AEPI_STORE = 0, AEPI_XIELU = 1, AEPI_SWIGLU = 2, AEPI_RELU2 = 3, AEPI_CLAMP_GLU = 4 };
 
 struct GemmAnyArgs {
     const float* A; int lda;
@@ -20,7 +22,8 @@ struct GemmAnyArgs {
     const float* bias;        // [N] or nullptr
     float* C; int ldc;
     int M, N, K;
-    float act_a, act_b;       // AEPI_XIELU: alpha_p, alpha_n
+    float act_a, act_b;       // AEPI_XIELU: alpha_p, alpha_n; AEPI_CLAMP_GLU: limit, slope
+    int glu = 0;              // which gated unit the gate / up epilogue forms: 0 silu(gate) * up, 1 the clamped one (set by gemm_any)
     // Batches (grid z).  Batch b reads A + ai * a_bs and W + wi * w_bs (bias + wi * N) and writes C + b * c_bs, ai = a_index ? a_index[b] : b,
     // wi = w_index ? w_index[b] : b (both device arrays): per-head products (a_bs = the head's column offset), one expert's matrix per row, ...
     int batch = 1;
@@ -69,7 +72,7 @@ __device__ __forceinline__ float any_epilogue(const GemmAnyArgs& g, float v, int
 
 __device__ __forceinline__ float any_swiglu(const GemmAnyArgs& g, float gate, float up, int n) {
     if (g.bias) { gate += g.bias[n]; up += g.bias[n + 1]; }
-    return silu_f(gate) * up;
+    return g.glu ? clamp_glu_f(gate, up, g.act_a, g.act_b) : silu_f(gate) * up;
 }
 
 template <typename WT, int EPI>
@@ -286,8 +289,11 @@ inline void gemm_any_launch(cudaStream_t st, const GemmAnyArgs& g, int num_sms) 
 }
 
 // fp32_weights: W holds floats, else bf16
-inline void gemm_any(cudaStream_t st, int epi, bool fp32_weights, const GemmAnyArgs& g, int num_sms) {
+inline void gemm_any(cudaStream_t st, int epi, bool fp32_weights, const GemmAnyArgs& g_in, int num_sms) {
+    GemmAnyArgs g = g_in;
     if (g.M == 0 || g.N == 0) return;
+    g.glu = epi == AEPI_CLAMP_GLU ? 1 : 0;
+    if (epi == AEPI_CLAMP_GLU) epi = AEPI_SWIGLU;
     AHA_REQUIRE(epi == AEPI_STORE || epi == AEPI_XIELU || epi == AEPI_SWIGLU || epi == AEPI_RELU2, "gemm_any: bad epilogue");
     AHA_REQUIRE(epi != AEPI_SWIGLU || g.N % 2 == 0, "gemm_any: the gate / up epilogue needs an even number of weight rows");
     AHA_REQUIRE(g.batch >= 1 && g.batch <= 65535, "gemm_any: bad batch count");

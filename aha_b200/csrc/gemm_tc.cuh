@@ -179,7 +179,7 @@ struct GemmTcArgs {
     __half* out_lo = nullptr;   // next GEMM instead of fp32 C (EPI_STORE / EPI_ACT / EPI_SWIGLU)
     int ldo = 0;
     int bf16 = 0;      // 1: A (hi / lo) and W hold bfloat16 instead of fp16 (same tiles and pipeline, the instruction descriptor names the format)
-    float act_a = 0.f, act_b = 0.f;   // ACT_XIELU: alpha_p, alpha_n
+    float act_a = 0.f, act_b = 0.f;   // ACT_XIELU: alpha_p, alpha_n; EPI_SWIGLU with act == ACT_CLAMP_GLU: limit, slope of the clamped gated unit
     int group_m = 8;   // persistent kernel: tiles are walked in bands of group_m row blocks (n outer, m inner) so that one wave of CTAs shares few A and W tiles
     // Grouped mode (gemm_tc_kernel only): the rows of A and C are cut into `groups` consecutive ranges by grp_offsets (device, [groups + 1]);
     // range e multiplies with rows [e N, (e + 1) N) of the stacked weight matrix the W descriptor covers.  blockIdx.y walks the ranges' row
@@ -211,7 +211,7 @@ __device__ __forceinline__ void tc_epilogue_store(const GemmTcArgs& g, float (&v
     if (EPI == EPI_SWIGLU) {
         float r[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) r[j] = silu_f(v[2 * j]) * v[2 * j + 1];
+        for (int j = 0; j < 16; ++j) r[j] = g.act == ACT_CLAMP_GLU ? clamp_glu_f(v[2 * j], v[2 * j + 1], g.act_a, g.act_b) : silu_f(v[2 * j]) * v[2 * j + 1];
         if (g.out_hi) {
             const size_t o = (size_t)row * g.ldo + n / 2;
             tc_store_split8(r, g.out_hi + o, g.out_lo + o);

@@ -187,14 +187,23 @@ static __global__ void argmax_final_kernel(const float* __restrict__ pmax, const
 
 
 // ---- kernels of the ragged (varlen) path -------------------------------------------------------------------------------------------
-// Row gather from an embedding table stored as fp32 or bf16 (both widen exactly to the fp32 residual stream).
+// Row gather from an embedding table stored as fp32 or bf16 (both widen exactly to the fp32 residual stream), times `scale`.  pos_table
+// ([max_pos, H] fp32): row tok_pos[s] of a learned position table is added (unscaled).  copy: the rows are stored there as well.
 template <typename WT>
-static __global__ void embed_gather_any_kernel(const uint32_t* __restrict__ ids, const WT* __restrict__ table, float* __restrict__ out, int H, int V, float scale = 1.f) {
+static __global__ void embed_gather_any_kernel(const uint32_t* __restrict__ ids, const WT* __restrict__ table, float* __restrict__ out, int H, int V, float scale = 1.f,
+                                               const float* __restrict__ pos_table = nullptr, const int* __restrict__ tok_pos = nullptr, int max_pos = 0,
+                                               float* __restrict__ copy = nullptr) {
     const int s = blockIdx.x;
     uint32_t id = ids[s];
     if (id >= (uint32_t)V) id = V - 1;  // the host validates; keep the kernel memory-safe regardless
     const WT* row = table + (size_t)id * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)s * H + i] = (float)row[i] * scale;
+    const float* prow = pos_table ? pos_table + (size_t)min(max(tok_pos[s], 0), max_pos - 1) * H : nullptr;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = (float)row[i] * scale;
+        if (prow) v += prow[i];
+        out[(size_t)s * H + i] = v;
+        if (copy) copy[(size_t)s * H + i] = v;
+    }
 }
 
 // Post-norm residual step with a scalar gain: x[row] += g * y[row] / sqrt(mean(y[row]^2) + eps).  The gain is ONE number (read from

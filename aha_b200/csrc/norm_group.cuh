@@ -6,6 +6,8 @@
 //                          (in + skip_w[channel / skip_span] * skip) * silu(gate) -- a state-space layer's D x term and output gate --,
 //                          and the residual update  out += mult * normed  (post-norm of a sublayer) instead of a store.
 //   post_pre_norm_kernel   the residual update after a sublayer and the norm before the next one in one launch
+//   sum_residual_norm_kernel  the end of a PARALLEL layer (both sublayers read one normed row): x += y_a + y_b, optionally a further row
+//                          added after that (what a pass of looped layers starts from), and the next layer's norm, in one launch
 //   short_conv_kernel      causal convolution over time on every channel, y_t = sum_j w[c][j] u_{t - taps + 1 + j} (+ bias) (silu) (+ u_t);
 //                          the taps - 1 inputs before a step are the sequence's state ("tail") in its slot, zeros before position 0.
 //                          An entry of one token moves its tail along in the same launch; short_conv_tail_kernel does it for longer entries.
@@ -137,7 +139,7 @@ static __global__ void post_pre_norm_reg_kernel(PostPreNormArgs a) {
                     s.x = fmaf(w, v.x, s.x); s.y = fmaf(w, v.y, s.y); s.z = fmaf(w, v.z, s.z); s.w = fmaf(w, v.w, s.w);
                 }
                 if (a.mix_shared) {
-                    const float g = sigmoid_f(a.mix_gate[r * a.mix_ldg]);
+                    const float g = a.mix_gate ? sigmoid_f(a.mix_gate[r * a.mix_ldg]) : 1.f;
                     const float4 v = reinterpret_cast<const float4*>(a.mix_shared + r * a.C)[c];
                     s.x = fmaf(g, v.x, s.x); s.y = fmaf(g, v.y, s.y); s.z = fmaf(g, v.z, s.z); s.w = fmaf(g, v.w, s.w);
                 }
@@ -190,6 +192,121 @@ inline void post_pre_norm(cudaStream_t st, const PostPreNormArgs& a, int rows) {
         else if (nv <= 4) post_pre_norm_reg_kernel<4><<<rows, threads, 0, st>>>(a);
         else post_pre_norm_reg_kernel<8><<<rows, threads, 0, st>>>(a);
     } else post_pre_norm_kernel<<<rows, threads, 0, st>>>(a);
+    AHA_CUDA_CHECK(cudaGetLastError());
+}
+
+// The end of a parallel layer and the start of the next in ONE launch:
+//     x += y_a + y_b;   (trace: x as it is now goes there)   x += inject;   h = rms_norm(x) * w_next
+// y_b may be formed on the way from a token's expert rows (as PostPreNormArgs::mix_*; no gate: the shared row is added as it is).  Every
+// part but x and y_a is optional.  One block per row; with the row in registers (C % 4 == 0, C <= 4 NV blockDim) everything is read once.
+struct SumResidualNormArgs {
+    float* x;                  // [T, C] residual stream, updated in place
+    const float* y_a;          // [T, C]
+    const float* y_b = nullptr;
+    const float* mix_rows = nullptr; int mix_top = 0;
+    const float* mix_w = nullptr; int mix_ldw = 0;
+    const float* mix_shared = nullptr; const float* mix_gate = nullptr; int mix_ldg = 0;
+    float* trace = nullptr;    // [T, C]
+    const float* inject = nullptr;   // [T, C]
+    const float* w_next = nullptr;   // [C]; nullptr: no norm
+    float* h = nullptr;        // [T, C]
+    float eps = 0.f;
+    int C = 0;
+};
+
+template <int NV>
+static __global__ void sum_residual_norm_reg_kernel(SumResidualNormArgs a) {
+    __shared__ float red[32];
+    const size_t r = blockIdx.x;
+    const int C4 = a.C >> 2;
+    float4* x4 = reinterpret_cast<float4*>(a.x + r * a.C);
+    const float4* __restrict__ ya = reinterpret_cast<const float4*>(a.y_a + r * a.C);
+    float4 xv[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        xv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < C4) {
+            float4 v = x4[c];
+            const float4 p = ya[c];
+            float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (a.y_b) q = reinterpret_cast<const float4*>(a.y_b + r * a.C)[c];
+            else if (a.mix_rows) {
+                for (int k = 0; k < a.mix_top; ++k) {
+                    const float w = a.mix_w[r * a.mix_ldw + k];
+                    const float4 e = reinterpret_cast<const float4*>(a.mix_rows + (r * a.mix_top + k) * a.C)[c];
+                    q.x = fmaf(w, e.x, q.x); q.y = fmaf(w, e.y, q.y); q.z = fmaf(w, e.z, q.z); q.w = fmaf(w, e.w, q.w);
+                }
+                if (a.mix_shared) {
+                    const float g = a.mix_gate ? sigmoid_f(a.mix_gate[r * a.mix_ldg]) : 1.f;
+                    const float4 e = reinterpret_cast<const float4*>(a.mix_shared + r * a.C)[c];
+                    q.x = fmaf(g, e.x, q.x); q.y = fmaf(g, e.y, q.y); q.z = fmaf(g, e.z, q.z); q.w = fmaf(g, e.w, q.w);
+                }
+            }
+            v.x += p.x + q.x; v.y += p.y + q.y; v.z += p.z + q.z; v.w += p.w + q.w;
+            if (a.trace) reinterpret_cast<float4*>(a.trace + r * a.C)[c] = v;
+            if (a.inject) {
+                const float4 j = reinterpret_cast<const float4*>(a.inject + r * a.C)[c];
+                v.x += j.x; v.y += j.y; v.z += j.z; v.w += j.w;
+            }
+            x4[c] = v;
+            xv[i] = v;
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+    }
+    if (!a.w_next) return;
+    ss = block_sum(ss, red);
+    const float sc = 1.0f / sqrtf(ss / (float)a.C + a.eps);
+    float4* h4 = reinterpret_cast<float4*>(a.h + r * a.C);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < C4) {
+            const float4 w = reinterpret_cast<const float4*>(a.w_next)[c];
+            h4[c] = make_float4(xv[i].x * sc * w.x, xv[i].y * sc * w.y, xv[i].z * sc * w.z, xv[i].w * sc * w.w);
+        }
+    }
+}
+
+// any C and alignment: a thread rereads only what it wrote itself
+static __global__ void sum_residual_norm_kernel(SumResidualNormArgs a) {
+    __shared__ float red[32];
+    const size_t r = blockIdx.x;
+    float* x = a.x + r * a.C;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < a.C; c += blockDim.x) {
+        float q = 0.f;
+        if (a.y_b) q = a.y_b[r * a.C + c];
+        else if (a.mix_rows) {
+            for (int k = 0; k < a.mix_top; ++k) q = fmaf(a.mix_w[r * a.mix_ldw + k], a.mix_rows[(r * a.mix_top + k) * a.C + c], q);
+            if (a.mix_shared) q = fmaf(a.mix_gate ? sigmoid_f(a.mix_gate[r * a.mix_ldg]) : 1.f, a.mix_shared[r * a.C + c], q);
+        }
+        float v = x[c] + (a.y_a[r * a.C + c] + q);
+        if (a.trace) a.trace[r * a.C + c] = v;
+        if (a.inject) v += a.inject[r * a.C + c];
+        x[c] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!a.w_next) return;
+    ss = block_sum(ss, red);
+    const float sc = 1.0f / sqrtf(ss / (float)a.C + a.eps);
+    for (int c = threadIdx.x; c < a.C; c += blockDim.x) a.h[r * a.C + c] = x[c] * sc * a.w_next[c];
+}
+
+inline void sum_residual_norm(cudaStream_t st, const SumResidualNormArgs& a, int rows) {
+    if (rows == 0) return;
+    const int threads = post_pre_norm_threads(a.C, rows);
+    const int nv = (a.C / 4 + threads - 1) / threads;
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool reg = post_pre_norm_in_registers(a.C, rows) && al(a.x) && al(a.y_a) && al(a.y_b) && al(a.mix_rows) && al(a.mix_shared) && al(a.trace) && al(a.inject) &&
+                     al(a.w_next) && al(a.h);
+    if (reg) {
+        if (nv <= 1) sum_residual_norm_reg_kernel<1><<<rows, threads, 0, st>>>(a);
+        else if (nv <= 2) sum_residual_norm_reg_kernel<2><<<rows, threads, 0, st>>>(a);
+        else if (nv <= 4) sum_residual_norm_reg_kernel<4><<<rows, threads, 0, st>>>(a);
+        else sum_residual_norm_reg_kernel<8><<<rows, threads, 0, st>>>(a);
+    } else sum_residual_norm_kernel<<<rows, threads, 0, st>>>(a);
     AHA_CUDA_CHECK(cudaGetLastError());
 }
 

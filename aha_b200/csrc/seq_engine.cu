@@ -1,10 +1,13 @@
 // seq_engine.cu -- the layered sequence engine (see seq_engine.h): a model is a list of layers read from config.json, each a mixer and
-// an optional feed-forward inside one of two layer templates (chosen by the config's "architecture"):
+// an optional feed-forward inside one of three layer templates (chosen by the config's "architecture"):
 //     post-norm   x += norm1(mixer(x));   x += norm2(ff(x))                      norms with ONE scalar gain on the sublayer outputs
 //     sandwich    x += m * norm1b(mixer(u)),  u = h + conv1(h),  h = norm1(x)    and the same around the feed-forward: RMS norms in groups with a
 //                 gain per channel before AND after each sublayer, a short causal convolution over time on what the sublayer reads (its last
 //                 inputs are state of the sequence), a residual multiplier m; a span of layers may run several times in a row with the same
 //                 weights ("loop"), every pass with a state of its own and a learned vector added to the stream before it
+//     parallel    x += mixer(h) + ff(h),  h = norm1(x)                           ONE norm (gain stored as an offset from one) whose output both sublayers
+//                 read; a learned position vector joins the scaled embedding; in a loop the embedding output is added to the stream again
+//                 before every pass but the first
 // run by ONE ragged step function: the tokens of all entries of a step are packed into [T, width] fp32 rows, every Linear is one
 // GEMM over all rows, and the mixers' sequence kernels (recurrence.cuh, attention_window.cuh) take the RaggedBatch description.
 // Mixers and feed-forwards are looked up by name in a registry, each with its sizes and constants read from its config entry:
@@ -24,6 +27,12 @@
 //     "latent_attention"  as above without a rotated part: queries through a normed latent of their own, a sliding window
 //     "dense"      W_down relu(W_up x)^2
 //     "moe"        softmax router, the `top` best scores weigh their experts unrenormalised, a shared expert behind a sigmoid gate  (moe_router.cuh)
+// The Gomerax design (parallel template, the embedding table also the output projection) has
+//     "latent_attention"  as above with a query latent, a rotated part (plain rotary frequencies), a sliding window and a learned sink per head in
+//                  the softmax denominator
+//     "dense"      W_down (silu(W_gate h) * W_up h), biases on all three
+//     "moe"        softmax router; a learned correction enters the choice only, experts are chosen from the best groups of neighbours, weights are
+//                  renormalised over the chosen experts and scaled; experts and the shared expert are clamped gated units      (moe_router.cuh)
 // Memory: one free list of 32-token pages serves every layer that owns keys / values (K pages [page][G][32][D], V pages
 // [page][G][32][Dv], fp32); a sequence additionally owns a state slot (recurrent states, convolution tails, sampler state).
 // Precision: the residual stream, norms, gates, recurrent state, scores and softmax are fp32 in both modes; the Linear layers
@@ -117,9 +126,15 @@ struct Engine final : SeqEngine {
         float *conv1 = nullptr, *conv2 = nullptr;                   // [W, taps] input convolutions
         float *tails1 = nullptr, *tails2 = nullptr;                 // [slots][taps - 1][W] their state, per run
         int pass = -1;                                              // >= 0: the run opens this pass of the loop (loop_step row added first)
+        bool reinject = false;                                      // parallel template: the run opens a pass after the first, the embedding output is added first
     };
     std::vector<LayerRec> layers;
     bool sandwich = false;
+    bool parallel = false;         // the parallel template (one norm per layer, both sublayers read it, their outputs are summed into the stream)
+    float gain_offset = 0.f;       // norm gains are stored as offsets from this number
+    float* pos_table = nullptr; int max_positions = 0;   // [max_positions, W] learned position rows added to the embedding
+    float* x0 = nullptr;           // [T, W] the embedding output of the step, kept for the passes of a loop that add it again
+    float* y2 = nullptr;           // [T, W] parallel template: the feed-forward's output beside the mixer's
     std::string design;            // config.json's "architecture", lower case
     int norm_groups = 1, conv_taps = 0;
     float resid_mult = 1.f, embed_scale = 1.f, logit_scale = 1.f;
@@ -139,6 +154,16 @@ struct Engine final : SeqEngine {
         auto it = vec_cache.find(name);
         if (it != vec_cache.end()) return it->second;
         return vec_cache[name] = upload_vec(c, wt, name, n);
+    }
+    // a norm gain as the kernels apply it: gain_offset + the stored vector
+    float* gain_vec(const WeightTable& wt, const std::string& name, size_t n) {
+        if (gain_offset == 0.f) return vec(wt, name, n);
+        const std::string key = name + " (+offset)";
+        auto it = vec_cache.find(key);
+        if (it != vec_cache.end()) return it->second;
+        std::vector<float> v = wt.vec_f32(name, n);
+        for (auto& g : v) g += gain_offset;
+        return vec_cache[key] = upload(c, v);
     }
     std::vector<Sublayer*> mixer_of_layer;   // for kv_from lookups while building
     uint64_t wbytes = 0;
@@ -250,7 +275,9 @@ struct Engine final : SeqEngine {
         return Lw;
     }
     // A matrix [N, K] in the engine's storage type whose row n is row src[n].second of tensor src[n].first ([., K]): stacks, interleavings.
-    LinearAny load_rows(const WeightTable& wt, const std::string& key, const std::vector<std::pair<const aha_tensor_desc*, int>>& src, int K) {
+    // bias_src (optional, one entry per row): element .second of vector .first is the row's bias
+    LinearAny load_rows(const WeightTable& wt, const std::string& key, const std::vector<std::pair<const aha_tensor_desc*, int>>& src, int K,
+                        const std::vector<std::pair<const aha_tensor_desc*, int>>* bias_src = nullptr) {
         auto hit = lin_cache.find(key);
         if (hit != lin_cache.end()) return hit->second;
         LinearAny Lw;
@@ -271,6 +298,16 @@ struct Engine final : SeqEngine {
             }
         }
         Lw.w = upload(c, st);
+        if (bias_src) {
+            AHA_REQUIRE(bias_src->size() == src.size(), "load_rows: one bias entry per row");
+            std::vector<float> b(src.size());
+            for (size_t n = 0; n < src.size(); ++n) {
+                const aha_tensor_desc& d = *(*bias_src)[n].first;
+                AHA_REQUIRE((size_t)(*bias_src)[n].second < WeightTable::numel(d), std::string("bias '") + (d.name ? d.name : "?") + "' is smaller than the config says");
+                b[n] = WeightTable::at(d, (size_t)(*bias_src)[n].second);
+            }
+            Lw.b = upload(c, b);
+        }
         lin_cache[key] = Lw;
         return Lw;
     }
@@ -303,8 +340,9 @@ struct Engine final : SeqEngine {
             if (!Wt.has_tmap) { Wt.tmap = make_tmap_f16(Wt.w, (uint64_t)Wt.N, (uint64_t)Wt.K); Wt.has_tmap = true; }   // 16-bit elements: the copy is bitwise
             GemmTcArgs t{};
             t.bias = Wt.b; t.resid = nullptr; t.ldr = 0; t.C = C; t.ldc = ldc; t.M = M; t.N = Wt.N; t.K = Wt.K;
-            t.act = epi == AEPI_XIELU ? ACT_XIELU : (epi == AEPI_RELU2 ? ACT_RELU2 : ACT_NONE); t.act_a = a0; t.act_b = a1; t.bf16 = 1; t.group_m = std::max(1, c.gemm_group_m);
-            const int e = (epi == AEPI_XIELU || epi == AEPI_RELU2) ? EPI_ACT : (epi == AEPI_SWIGLU ? EPI_SWIGLU : EPI_STORE);
+            t.act = epi == AEPI_XIELU ? ACT_XIELU : (epi == AEPI_RELU2 ? ACT_RELU2 : (epi == AEPI_CLAMP_GLU ? ACT_CLAMP_GLU : ACT_NONE));
+            t.act_a = a0; t.act_b = a1; t.bf16 = 1; t.group_m = std::max(1, c.gemm_group_m);
+            const int e = (epi == AEPI_XIELU || epi == AEPI_RELU2) ? EPI_ACT : ((epi == AEPI_SWIGLU || epi == AEPI_CLAMP_GLU) ? EPI_SWIGLU : EPI_STORE);
             if (c.gemm_pair && Wt.N >= 256 && M >= 1024) gemm_tc3_launch(c.stream, e, hi, lo, Wt.tmap, t, c.num_sms);
             else if (c.gemm_wide && Wt.N >= 256) {
                 if (!Wt.has_tmap256) { Wt.tmap256 = make_tmap_f16_rows(Wt.w, (uint64_t)Wt.N, (uint64_t)Wt.K, 256); Wt.has_tmap256 = true; }
@@ -435,6 +473,8 @@ struct Engine final : SeqEngine {
         const int E = (int)pieces.size();
         int T = 0;
         for (auto& p : pieces) T += p.cnt;
+        if (pos_table)
+            for (auto& p : pieces) AHA_REQUIRE(seqs[ents[p.ent].slot].pos + p.cnt <= max_positions, "step: a sequence would grow beyond the model's " + std::to_string(max_positions) + " learned positions");
         for (auto& p : pieces) map_pages(ents[p.ent].slot, seqs[ents[p.ent].slot].pos + p.cnt);
         // ---- metadata: tokens | fb_slot | tok_entry | tok_pos | ent_start | ent_pos0 | ent_slot | rows
         if (meta_pending) { AHA_CUDA_CHECK(cudaEventSynchronize(ev_meta)); meta_pending = false; }
@@ -531,13 +571,38 @@ struct Engine final : SeqEngine {
         const int T = rb.T;
         pre_ready = nullptr; mix_pending = false;
         if (any_fb) { feedback_tokens_kernel<<<ceil_div(T, 256), 256, 0, st>>>(reinterpret_cast<uint32_t*>(d_meta), d_fb, d_states, T); c.cnt.kernels++; }
-        if (fp32) embed_gather_any_kernel<float><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const float*>(embed), x, W, V, embed_scale);
-        else embed_gather_any_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const __nv_bfloat16*>(embed), x, W, V, embed_scale);
+        if (fp32) embed_gather_any_kernel<float><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const float*>(embed), x, W, V, embed_scale, pos_table, rb.tok_pos, max_positions, x0);
+        else embed_gather_any_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(rb.tokens, reinterpret_cast<const __nv_bfloat16*>(embed), x, W, V, embed_scale, pos_table, rb.tok_pos, max_positions, x0);
         c.cnt.kernels++;
         const int norm_threads = T <= 8 ? std::min(1024, std::max(256, (W / 2 + 31) / 32 * 32)) : 256;      // a decode step has few blocks: more threads for each
         StepView v{this, rb, x, y, h_meta + 4 * Tmax, h_meta + 4 * Tmax + (slots + 1), h_meta + 4 * Tmax + (slots + 1) + slots, cur_span};
+        if (parallel) {      // the first layer's norm; every later one rides with the residual update before it
+            tic("norm", 4.0 * T * W, 8.0 * T * W);
+            GroupNormArgs n{};
+            n.in = x; n.ld_in = W; n.w = layers[0].pre1; n.eps = eps; n.C = W; n.groups = 1; n.out = hnorm; n.ld_out = W;
+            group_rmsnorm(st, n, T); c.cnt.kernels++;
+            toc();
+        }
         for (int l = 0; l < L; ++l) {
             LayerRec& Ly = layers[l];
+            if (parallel) {
+                v.x = hnorm; v.y = y;
+                Ly.mixer->run(v);
+                if (Ly.ff) { v.y = y2; Ly.ff->run(v); }
+                const LayerRec* nx = l + 1 < L ? &layers[l + 1] : nullptr;
+                tic("residual sum + next norm", 6.0 * T * W, (nx ? 20.0 : 12.0) * T * W);
+                SumResidualNormArgs a{};
+                a.x = x; a.y_a = y; a.eps = eps; a.C = W;
+                if (mix_pending) {
+                    a.mix_rows = mix.rows; a.mix_top = mix.top; a.mix_w = mix.weights; a.mix_ldw = mix.ld_w; a.mix_shared = mix.shared; a.mix_gate = mix.gate; a.mix_ldg = mix.ld_gate;
+                    mix_pending = false;
+                } else if (Ly.ff) a.y_b = y2;
+                if (trace) a.trace = trace_buf + (size_t)l * Tmax * W;
+                if (nx) { a.inject = nx->reinject ? x0 : nullptr; a.w_next = nx->pre1; a.h = hnorm; }
+                sum_residual_norm(st, a, T); c.cnt.kernels++;
+                toc();
+                continue;
+            }
             if (sandwich) {
                 if (Ly.pass >= 0) {
                     add_row_vector_kernel<<<(unsigned)(((size_t)T * W + 255) / 256), 256, 0, st>>>(x, loop_step + (size_t)Ly.pass * W, W, (size_t)T * W); c.cnt.kernels++;
@@ -572,7 +637,7 @@ struct Engine final : SeqEngine {
         AHA_CUDA_CHECK(cudaGetLastError());
         for (int r0 = 0; r0 < nrows; r0 += Rmax) {
             const int nr = std::min(Rmax, nrows - r0);
-            if (sandwich) {
+            if (sandwich || parallel) {
                 GroupNormArgs n{};
                 n.in = x; n.ld_in = W; n.rows = d_rows + r0; n.w = final_w; n.eps = eps; n.C = W; n.groups = norm_groups; n.out = hn; n.ld_out = W; n.mult = logit_scale;
                 group_rmsnorm(st, n, nr);
@@ -641,7 +706,7 @@ struct Engine final : SeqEngine {
     const float* pre_ready = nullptr;      // the gain of the pre-norm whose result hnorm already holds
     // routed experts of a decode-sized step may leave their weighted sum to the launch that follows (see PostPreNormArgs::mix_*)
     WeightedCombineArgs mix{}; bool mix_pending = false;
-    bool can_defer_mix(int T) const { return sandwich && norm_groups == 1 && post_pre_norm_in_registers(W, T); }
+    bool can_defer_mix(int T) const { return parallel || (sandwich && norm_groups == 1 && post_pre_norm_in_registers(W, T)); }
     void sublayer_output(int T, const float* gain, const float* next_pre = nullptr) {
         const bool fuse = next_pre && norm_groups == 1 && !out_src;
         if (mix_pending && !fuse) {          // nothing to ride with (the last sublayer of the model): the combine kernel after all
@@ -960,6 +1025,33 @@ struct DenseFF final : Sublayer {
     }
 };
 
+// W_down (silu(W_gate h) * (W_up h)) with optional biases on all three ('.gate.b', '.up.b', '.down.b').  The gate and up rows are interleaved into
+// one matrix, so that the gated unit is the product's epilogue.
+struct GatedDenseFF final : Sublayer {
+    Engine& E;
+    int ff;
+    LinearAny gu, down;
+    GatedDenseFF(Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) : E(e) {
+        ff = cfg.integer("ff");
+        AHA_REQUIRE(ff >= 1, "dense: bad size");
+        wt.expect(p + "gate", {ff, E.W}); wt.expect(p + "up", {ff, E.W});
+        std::vector<std::pair<const aha_tensor_desc*, int>> rows, bias;
+        const bool has_bias = wt.has(p + "gate.b") && wt.has(p + "up.b");
+        for (int j = 0; j < ff; ++j) {
+            rows.push_back({&wt.get(p + "gate"), j}); rows.push_back({&wt.get(p + "up"), j});
+            if (has_bias) { bias.push_back({&wt.get(p + "gate.b"), j}); bias.push_back({&wt.get(p + "up.b"), j}); }
+        }
+        gu = E.load_rows(wt, p + "gate/up", rows, E.W, has_bias ? &bias : nullptr);
+        down = E.load_linear(wt, {p + "down"}, {E.W}, ff, {p + "down.b"});
+    }
+    int proj_cols() const override { return ff; }
+    int inner_cols() const override { return 0; }
+    void run(const StepView& v) override {
+        E.gemm(AEPI_SWIGLU, v.x, E.W, gu, E.proj, ff, v.rb.T);
+        E.gemm(AEPI_STORE, E.proj, ff, down, v.y, E.W, v.rb.T);
+    }
+};
+
 // Gated linear attention: q = W_q h / sqrt(dim), k = W_k h, v = W_v h, a decay per key channel alpha = sigmoid(z)^(1 / tau) with
 // z = W_a2 (W_a1 h) + b (a low-rank projection); per head S <- diag(alpha) S + k v^T, o = S^T q; o is RMS-normed per head (gain over vdim
 // shared by the heads), multiplied by silu(W_g h) and projected by W_o.  The state is fp32 in the slot pool.
@@ -1089,7 +1181,7 @@ struct Mamba2Mixer final : Sublayer {
 // Latent attention (see attention_latent.cuh): the cache holds [latent | rotated key part] per token; a head's query is absorbed through
 // W_uk, its output expanded through W_uv; causal, ordinary softmax.  By the layer's config entry and tensors: a rotated part (rot_dim > 0,
 // YaRN rotary), queries through a normed latent of their own ('q_rank': q = W_uq norm(W_dq h)) or straight from the input ('.q'), a sliding
-// window ('mask.size'), a sigmoid output gate from the mixer's input ('.g').
+// window ('mask.size'), a sigmoid output gate from the mixer's input ('.g'), a learned sink per head in the softmax denominator ('.sink').
 struct LatentAttentionMixer final : Sublayer {
     Engine& E;
     int H, D, R, Dv, rank, q_rank = 0, window = 0;
@@ -1097,7 +1189,7 @@ struct LatentAttentionMixer final : Sublayer {
     LinearAny in, out, uq, uk_t, uv, ukv;
     bool can_expand = false, has_gate = false;
     int ld = 0, q_off = 0, dkv_off = 0, g_off = 0, n_freq = 0;
-    float *c_norm = nullptr, *q_norm = nullptr, *freq = nullptr;
+    float *c_norm = nullptr, *q_norm = nullptr, *freq = nullptr, *sink = nullptr;
     PagedKV kv;
     LatentAttentionMixer(Engine& e, const Json& mx, const WeightTable& wt, const std::string& p) : E(e) {
         H = mx.integer("heads"); D = mx.integer("dim"); R = mx.integer_or("rot_dim", 0); Dv = mx.integer("vdim"); rank = mx.integer("kv_rank");
@@ -1107,6 +1199,7 @@ struct LatentAttentionMixer final : Sublayer {
         window = mx.has("mask") ? mx.at("mask").integer("size") : 0;
         AHA_REQUIRE(q_rank >= 0 && window >= 0, "latent attention: q_rank and mask.size must be positive");
         has_gate = wt.has(p + "g");
+        if (wt.has(p + "sink")) sink = E.vec(wt, p + "sink", (size_t)H);
         {   // one product for everything that reads the mixer's input: [q or its latent | dkv | gate]
             const int first = q_rank > 0 ? q_rank : H * (D + R);
             std::vector<std::string> names{p + (q_rank > 0 ? "dq" : "q"), p + "dkv"};
@@ -1226,6 +1319,7 @@ struct LatentAttentionMixer final : Sublayer {
         if (!all_long) {
             WindowAttnArgs w{};
             w.q = E.qbuf; w.kv = kv; w.slopes = nullptr; w.scale = scale; w.window = window; w.gate = nullptr; w.out = E.inner; w.H = H; w.rb = v.rb;
+            w.sink = sink ? 1 : 0; w.sink_logit = sink;
             w.part = E.opt.seq_impl == 1 ? nullptr : E.attn_part;
             w.skip_from_n = any_long ? kLatentExpandMinTokens : 0;
             const int span = window > 0 ? std::min(window, v.span) : v.span;
@@ -1255,7 +1349,7 @@ struct LatentAttentionMixer final : Sublayer {
             f.kx = E.lat_kv; f.ld_k = ukv.N; f.k_head_stride = D;
             f.vx = E.lat_kv + (size_t)H * D; f.ld_v = ukv.N; f.v_head_stride = Dv;
             f.k_rot = E.lat_gather + rank; f.ld_kr = rank + R;
-            f.out = attn_out; f.ld_o = H * Dv; f.t0 = v.h_ent_start[e]; f.n = n; f.pos0 = rel0; f.D = D; f.R = R; f.Dv = Dv; f.scale = scale; f.window = window;
+            f.out = attn_out; f.ld_o = H * Dv; f.t0 = v.h_ent_start[e]; f.n = n; f.pos0 = rel0; f.D = D; f.R = R; f.Dv = Dv; f.scale = scale; f.window = window; f.sink = sink;
             double pairs = 0;
             for (int k = 0; k < n; ++k) pairs += window > 0 ? std::min(pos0 + k + 1, window) : pos0 + k + 1;
             if (expand_on_tc()) {
@@ -1419,39 +1513,70 @@ struct TableMoeFF final : Sublayer {
     }
 };
 
-// Mixture of experts chosen by a router (see moe_router.cuh): scores = softmax(W_router h) over all experts, the `top` best weigh their experts'
-// outputs unrenormalised; expert: W_down act(W_up h) without biases; an optional shared expert of the same form runs for every token and is
-// added times sigmoid(W_sg h).  The router and the shared gate are ONE fp32 product whatever the engine's mode; the experts' matrices are
-// stacked so that the products are batched (decode steps: one row per assignment with its expert's matrix) or grouped (assignments ordered by
-// expert on the device, one launch over all experts; on the tensor cores where the sizes tile).
+// What differs between the designs' routed feed-forwards; sizes, limits, groups and factors come from the layer's config entry.
+struct RoutedFlavor {
+    int act = AEPI_RELU2;            // the expert's unit: an activation on W_up h (AEPI_RELU2), or a gated unit of W_gate h and W_up h (AEPI_SWIGLU, AEPI_CLAMP_GLU)
+    float glu_slope = 1.f;           // AEPI_CLAMP_GLU: the gate passes through g * sigmoid(glu_slope * g); its limit is the expert's 'limit'
+    bool shared_gate = true;         // the shared expert is multiplied by sigmoid(W_sg h) (else added as it is)
+    bool correction = false;         // '.correction' is added to the scores for the choice
+    bool groups = false;             // router.groups {count, keep}: experts are chosen from the best groups only
+    bool renorm = false;             // the chosen scores are divided by their sum (+ floor), then ...
+    float floor = 0.f;
+    bool scaled = false;             // ... multiplied by router.scale
+    bool gated() const { return act == AEPI_SWIGLU || act == AEPI_CLAMP_GLU; }
+};
+
+// Mixture of experts chosen by a router (see moe_router.cuh): scores = softmax(W_router h) over all experts, the `top` best (by the flavour's
+// rule) weigh their experts' outputs; expert: W_down unit(h) without biases, the unit by the flavour; an optional shared expert of the same form
+// runs for every token and is added, times sigmoid(W_sg h) if the flavour has that gate.  The router and the shared gate are ONE fp32 product
+// whatever the engine's mode; the experts' matrices are stacked (gate and up rows interleaved for a gated unit) so that the products are batched
+// (decode steps: one row per assignment with its expert's matrix) or grouped (assignments ordered by expert on the device, one launch over all
+// experts; on the tensor cores where the sizes tile).
 struct RoutedMoeFF final : Sublayer {
     Engine& E;
-    int ff, ffs = 0, experts, top, act;
-    LinearAny up, down, sup, sdown;     // [experts * ff, W], [experts * W, ff]; the shared expert's
+    RoutedFlavor fl;
+    int ff, ffs = 0, experts, top, nup;  // nup: rows of an expert's first matrix (ff, or 2 ff interleaved)
+    float limit = 0.f, slimit = 0.f;     // clamp of the experts' / the shared expert's unit
+    LinearAny up, down, sup, sdown;     // [experts * nup, W], [experts * W, ff]; the shared expert's
     float* router = nullptr;             // [experts (+ 1), W] fp32: the router's rows, then the shared gate's
+    RouterRule rule;
     int n_router = 0, ldl = 0;
     int* tok_of_assign = nullptr;
     int* err = nullptr;
-    RoutedMoeFF(Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p, int activation) : E(e), act(activation) {
-        ff = cfg.at("expert").integer("ff"); experts = cfg.at("router").integer("experts"); top = cfg.at("router").integer("top");
+    RoutedMoeFF(Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p, RoutedFlavor flavor) : E(e), fl(flavor) {
+        const Json& rt = cfg.at("router");
+        ff = cfg.at("expert").integer("ff"); experts = rt.integer("experts"); top = rt.integer("top");
         AHA_REQUIRE(ff >= 1 && experts >= 1 && top >= 1 && top <= experts, "moe: bad sizes");
+        if (fl.act == AEPI_CLAMP_GLU) limit = (float)cfg.at("expert").number("limit");
+        nup = fl.gated() ? 2 * ff : ff;
         std::vector<std::pair<const aha_tensor_desc*, int>> s1, s2;
         for (int x = 0; x < experts; ++x) {
             const std::string q = p + "e" + std::to_string(x) + ".";
             wt.expect(q + "up", {ff, E.W}); wt.expect(q + "down", {E.W, ff});
-            for (int j = 0; j < ff; ++j) s1.push_back({&wt.get(q + "up"), j});
+            if (fl.gated()) wt.expect(q + "gate", {ff, E.W});
+            for (int j = 0; j < ff; ++j) {
+                if (fl.gated()) s1.push_back({&wt.get(q + "gate"), j});
+                s1.push_back({&wt.get(q + "up"), j});
+            }
             for (int j = 0; j < E.W; ++j) s2.push_back({&wt.get(q + "down"), j});
         }
-        up = E.load_rows(wt, p + "experts.up", s1, E.W);
+        up = E.load_rows(wt, p + (fl.gated() ? "experts.gate/up" : "experts.up"), s1, E.W);
         down = E.load_rows(wt, p + "experts.down", s2, ff);
         const bool shared = cfg.has("shared") && cfg.at("shared").kind == Json::Obj;
         if (shared) {
             ffs = cfg.at("shared").integer("ff");
             AHA_REQUIRE(ffs >= 1, "moe: bad shared expert size");
-            sup = E.load_linear(wt, {p + "shared.up"}, {ffs}, E.W, {});
+            if (fl.act == AEPI_CLAMP_GLU) slimit = (float)cfg.at("shared").number("limit");
+            if (fl.gated()) {
+                wt.expect(p + "shared.gate", {ffs, E.W}); wt.expect(p + "shared.up", {ffs, E.W});
+                std::vector<std::pair<const aha_tensor_desc*, int>> s3;
+                for (int j = 0; j < ffs; ++j) { s3.push_back({&wt.get(p + "shared.gate"), j}); s3.push_back({&wt.get(p + "shared.up"), j}); }
+                sup = E.load_rows(wt, p + "shared.gate/up", s3, E.W);
+            } else sup = E.load_linear(wt, {p + "shared.up"}, {ffs}, E.W, {});
             sdown = E.load_linear(wt, {p + "shared.down"}, {E.W}, ffs, {});
         }
-        n_router = experts + (shared ? 1 : 0);
+        const bool sgate = shared && fl.shared_gate;
+        n_router = experts + (sgate ? 1 : 0);
         ldl = n_router + top;      // a token's row: router logits | shared gate | the chosen experts' weights
         {
             const std::string key = p + "router (fp32)";
@@ -1459,10 +1584,19 @@ struct RoutedMoeFF final : Sublayer {
             if (hit != E.vec_cache.end()) router = hit->second;
             else {
                 std::vector<float> r = wt.vec_f32(p + "router", (size_t)experts * E.W);
-                if (shared) { auto g = wt.vec_f32(p + "shared.sg", (size_t)E.W); r.insert(r.end(), g.begin(), g.end()); }
+                if (sgate) { auto g = wt.vec_f32(p + "shared.sg", (size_t)E.W); r.insert(r.end(), g.begin(), g.end()); }
                 router = E.vec_cache[key] = upload(E.c, r);
             }
         }
+        if (fl.correction) rule.correction = E.vec(wt, p + "correction", (size_t)experts);
+        if (fl.groups && rt.has("groups") && rt.at("groups").kind == Json::Obj) {
+            rule.group_count = rt.at("groups").integer("count"); rule.group_keep = rt.at("groups").integer("keep");
+            AHA_REQUIRE(rule.group_count >= 1 && experts % rule.group_count == 0 && rule.group_keep >= 1 && rule.group_keep <= rule.group_count,
+                        "moe: router.groups.count must divide the experts, keep lie between 1 and count");
+            AHA_REQUIRE((int64_t)rule.group_keep * (experts / rule.group_count) >= top, "moe: the kept groups hold fewer than `top` experts");
+        }
+        rule.renorm = fl.renorm ? 1 : 0; rule.floor = fl.floor;
+        if (fl.scaled) rule.scale = (float)rt.number_or("scale", 1.0);
         std::vector<int> ta((size_t)kGraphMaxTokens * top);
         for (size_t i = 0; i < ta.size(); ++i) ta[i] = (int)(i / top);
         tok_of_assign = upload(E.c, ta);
@@ -1482,9 +1616,10 @@ struct RoutedMoeFF final : Sublayer {
         float* rows_out = E.inner; float* sout = E.inner + (size_t)E.Tmax * top * W;
         // router (+ shared gate): true fp32 on the CUDA cores in both modes
         E.tic("router", 2.0 * T * n_router * W, 4.0 * ((double)n_router * W + (double)T * (W + n_router)));
-        if (router_fused_supported(W, n_router)) {      // product, softmax and choice in one launch
+        if (router_fused_supported(W, n_router, rule.group_count)) {      // product, softmax and choice in one launch
             RouterFusedArgs r{};
             r.x = v.x; r.ldx = W; r.w = router; r.T = T; r.K = W; r.experts = experts; r.n_out = n_router; r.top = top; r.logits = logits; r.ld = ldl; r.expert_of = expert_of;
+            r.rule = rule;
             router_fused(st, r);
             E.c.cnt.kernels++;
         } else {
@@ -1493,6 +1628,7 @@ struct RoutedMoeFF final : Sublayer {
             gemm_any(st, AEPI_STORE, true, g, E.c.num_sms);
             RouterArgs r{};
             r.logits = logits; r.ld = ldl; r.T = T; r.experts = experts; r.top = top; r.expert_of = expert_of; r.weights = logits + n_router; r.ld_w = ldl;
+            r.rule = rule;
             router_topk(st, r);
             E.c.cnt.kernels += 2;
         }
@@ -1506,20 +1642,20 @@ struct RoutedMoeFF final : Sublayer {
             moe_table_route(st, r); E.c.cnt.kernels++;
             E.toc();
         }
-        const double wb = E.fp32 ? 4.0 : 2.0, used = std::min(A, experts);
+        const double wb = E.fp32 ? 4.0 : 2.0, used = std::min(A, experts), mats = fl.gated() ? 3.0 : 2.0;
         if (!rows && !E.fp32 && E.opt.gemm_impl != 1 && T >= kTcMinRows && W % kTcBK == 0 && ff % kTcBK == 0 && W % 32 == 0) {
             // both products on the tensor cores, ONE grouped launch each over the ordered rows
             __half* hi = E.c.split_buf((size_t)A * std::max(W, ff));
             __half* lo = hi + E.c.split_cap;
-            E.tic("expert linear (grouped, tcgen05, bf16 hi+lo)", 4.0 * A * ff * W, used * 2.0 * ff * W * wb + 4.0 * A * (2.0 * W + 2.0 * ff));
+            E.tic("expert linear (grouped, tcgen05, bf16 hi+lo)", 2.0 * mats * A * ff * W, used * mats * ff * W * wb + 4.0 * A * (2.0 * W + 2.0 * ff));
             gather_split_f32_to_bf16x2_kernel<<<(unsigned)(((size_t)A * W / 4 + 255) / 256), 256, 0, st>>>(v.x, W, sorted_tok, reinterpret_cast<__nv_bfloat16*>(hi), reinterpret_cast<__nv_bfloat16*>(lo), A, W);
             if (!up.has_tmap) { up.tmap = make_tmap_f16(up.w, (uint64_t)up.N, (uint64_t)up.K); up.has_tmap = true; }
             if (!down.has_tmap) { down.tmap = make_tmap_f16(down.w, (uint64_t)down.N, (uint64_t)down.K); down.has_tmap = true; }
             GemmTcArgs t{};
-            t.bias = nullptr; t.resid = nullptr; t.ldr = 0; t.C = hid; t.ldc = ff; t.M = A; t.N = ff; t.K = W; t.bf16 = 1;
-            t.act = act == AEPI_RELU2 ? ACT_RELU2 : ACT_NONE;
+            t.bias = nullptr; t.resid = nullptr; t.ldr = 0; t.C = hid; t.ldc = ff; t.M = A; t.N = nup; t.K = W; t.bf16 = 1;
+            t.act = fl.act == AEPI_RELU2 ? ACT_RELU2 : (fl.act == AEPI_CLAMP_GLU ? ACT_CLAMP_GLU : ACT_NONE); t.act_a = limit; t.act_b = fl.glu_slope;
             t.grp_offsets = offsets; t.groups = experts;
-            gemm_tc_grouped_launch(st, EPI_ACT, hi, lo, up.tmap, t);
+            gemm_tc_grouped_launch(st, fl.gated() ? EPI_SWIGLU : EPI_ACT, hi, lo, up.tmap, t);
             split_f32_to_bf16x2_kernel<<<(unsigned)(((size_t)A * ff / 4 + 255) / 256), 256, 0, st>>>(hid, ff, reinterpret_cast<__nv_bfloat16*>(hi), reinterpret_cast<__nv_bfloat16*>(lo), A, ff);
             t.C = rows_out; t.ldc = W; t.N = W; t.K = ff; t.act = ACT_NONE;
             gemm_tc_grouped_launch(st, EPI_STORE, hi, lo, down.tmap, t);
@@ -1527,10 +1663,10 @@ struct RoutedMoeFF final : Sublayer {
             E.toc();
         } else {
             GemmAnyArgs g{};
-            g.A = v.x; g.lda = W; g.W = up.w; g.C = hid; g.ldc = ff; g.N = ff; g.K = W; g.w_bs = (size_t)ff * W;
+            g.A = v.x; g.lda = W; g.W = up.w; g.C = hid; g.ldc = ff; g.N = nup; g.K = W; g.w_bs = (size_t)nup * W; g.act_a = limit; g.act_b = fl.glu_slope;
             if (rows) { g.M = 1; g.batch = A; g.a_index = tok_of_assign; g.a_bs = (size_t)W; g.c_bs = (size_t)ff; g.w_index = expert_of; }
             else { g.M = A; g.batch = experts; g.row_offsets = offsets; g.a_gather = sorted_tok; }
-            E.gemm_batched(rows ? "expert linear (decode rows)" : "expert linear (grouped, CUDA cores)", act, g, 2.0 * A * ff * W, used * ff * W * wb + 4.0 * A * (W + ff));
+            E.gemm_batched(rows ? "expert linear (decode rows)" : "expert linear (grouped, CUDA cores)", fl.act, g, 2.0 * A * nup * W, used * nup * W * wb + 4.0 * A * (W + ff));
             GemmAnyArgs d{};
             d.A = hid; d.lda = ff; d.W = down.w; d.C = rows_out; d.ldc = W; d.N = W; d.K = ff; d.w_bs = (size_t)W * ff;
             if (rows) { d.M = 1; d.batch = A; d.a_bs = (size_t)ff; d.c_bs = (size_t)W; d.w_index = expert_of; }
@@ -1538,12 +1674,12 @@ struct RoutedMoeFF final : Sublayer {
             E.gemm_batched(rows ? "expert linear (decode rows)" : "expert linear (grouped, CUDA cores)", AEPI_STORE, d, 2.0 * A * ff * W, used * ff * W * wb + 4.0 * A * (W + ff));
         }
         if (ffs > 0) {
-            E.gemm(act, v.x, W, sup, shid, ffs, T);
+            E.gemm(fl.act, v.x, W, sup, shid, ffs, T, slimit, fl.glu_slope);
             E.gemm(AEPI_STORE, shid, ffs, sdown, sout, W, T);
         }
         WeightedCombineArgs cb{};
         cb.rows = rows_out; cb.place_of = rows ? nullptr : place_of; cb.weights = logits + n_router; cb.ld_w = ldl;
-        cb.shared = ffs > 0 ? sout : nullptr; cb.gate = logits + experts; cb.ld_gate = ldl; cb.y = v.y; cb.C = W; cb.top = top; cb.total = (size_t)T * W;
+        cb.shared = ffs > 0 ? sout : nullptr; cb.gate = ffs > 0 && fl.shared_gate ? logits + experts : nullptr; cb.ld_gate = ldl; cb.y = v.y; cb.C = W; cb.top = top; cb.total = (size_t)T * W;
         if (rows && E.can_defer_mix(T)) { E.mix = cb; E.mix_pending = true; return; }      // summed by the norm + residual launch that follows
         E.tic("expert combine", 2.0 * (A + T) * W, 4.0 * (A + 2.0 * T) * W);
         moe_weighted_combine_kernel<<<(unsigned)((cb.total + 255) / 256), 256, 0, st>>>(cb);
@@ -1582,7 +1718,13 @@ const std::map<std::string, FFFactory>& ff_registry() {
         {"dense", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) { return std::unique_ptr<Sublayer>(new DenseFF(e, cfg, wt, p)); }},
         {"moe", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) { return std::unique_ptr<Sublayer>(new TableMoeFF(e, cfg, wt, p)); }},
         {"lupolorn:dense", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) { return std::unique_ptr<Sublayer>(new DenseFF(e, cfg, wt, p, AEPI_RELU2)); }},
-        {"lupolorn:moe", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) { return std::unique_ptr<Sublayer>(new RoutedMoeFF(e, cfg, wt, p, AEPI_RELU2)); }},
+        {"lupolorn:moe", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) { return std::unique_ptr<Sublayer>(new RoutedMoeFF(e, cfg, wt, p, RoutedFlavor())); }},
+        {"gomerax:dense", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) { return std::unique_ptr<Sublayer>(new GatedDenseFF(e, cfg, wt, p)); }},
+        {"gomerax:moe", [](Engine& e, const Json& cfg, const WeightTable& wt, const std::string& p) {
+             RoutedFlavor f;
+             f.act = AEPI_CLAMP_GLU; f.glu_slope = 1.702f; f.shared_gate = false; f.correction = true; f.groups = true; f.renorm = true; f.floor = 1e-20f; f.scaled = true;
+             return std::unique_ptr<Sublayer>(new RoutedMoeFF(e, cfg, wt, p, f));
+         }},
     };
     return r;
 }
@@ -1605,6 +1747,8 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
     for (auto& ch : arch) ch = (char)std::tolower((unsigned char)ch);
     e.design = arch;
     e.sandwich = arch == "gatuzen" || arch == "lupolorn";      // (Lupolorn: the same frame without groups, convolution or multiplier)
+    e.parallel = arch == "gomerax";
+    if (e.parallel) e.gain_offset = 1.f;                       // its norm gains are stored around zero
     // the runs: layers before the loop once, the loop's span `times` times, the rest once
     std::vector<std::pair<int, int>> runs;      // (layer, pass it opens or -1)
     {
@@ -1613,7 +1757,7 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
         if (cfg.has("loop")) {
             const Json& lp = cfg.at("loop");
             start = lp.integer("start"); stop = lp.integer("stop"); times = lp.integer("times");
-            AHA_REQUIRE(e.sandwich, "config.json: 'loop' is only known to the sandwich layer template");
+            AHA_REQUIRE(e.sandwich || e.parallel, "config.json: 'loop' is only known to the sandwich and parallel layer templates");
             AHA_REQUIRE(0 <= start && start <= stop && stop <= nl && times >= 1, "config.json: bad 'loop'");
         }
         for (int l = 0; l < start; ++l) runs.push_back({l, -1});
@@ -1621,9 +1765,10 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
             for (int t = 0; t < times; ++t)
                 for (int l = start; l < stop; ++l) runs.push_back({l, l == start ? t : -1});
         for (int l = stop; l < nl; ++l) runs.push_back({l, -1});
-        if (stop > start) e.loop_step = e.vec(wt, "loop.step", (size_t)times * e.W);
+        if (stop > start && e.sandwich) e.loop_step = e.vec(wt, "loop.step", (size_t)times * e.W);
     }
     e.L = (int)runs.size();
+    if (e.parallel && cfg.has("embedding")) e.embed_scale = (float)cfg.at("embedding").number_or("scale", 1.0);
     if (e.sandwich) {
         e.norm_groups = cfg.at("norm").integer_or("groups", 1);
         AHA_REQUIRE(e.norm_groups >= 1 && e.W % e.norm_groups == 0, "config.json: norm.groups must divide the width");
@@ -1640,8 +1785,15 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
     e.Rmax = std::min(e.Tmax, 128);
     e.embed = e.load_linear(wt, {"embed"}, {e.V}, e.W, {}).w;
     e.head = e.load_linear(wt, {wt.has("head") ? "head" : "embed"}, {e.V}, e.W, {});      // no 'head' tensor: the embedding table is the output projection
-    if (e.sandwich) e.final_w = e.vec(wt, "final.norm", (size_t)e.W);
+    if (e.sandwich || e.parallel) e.final_w = e.gain_vec(wt, "final.norm", (size_t)e.W);
     else e.final_gain = upload_scalar(e, wt, "final.norm");
+    if (e.parallel && wt.has("pos")) {      // learned position rows [max_positions, W]
+        const aha_tensor_desc& dp = wt.get("pos");
+        AHA_REQUIRE(dp.rank == 2 && dp.shape[1] == e.W && dp.shape[0] >= 1, "weight 'pos' must be [positions, width]");
+        e.max_positions = (int)dp.shape[0];
+        if (cfg.has("max_positions")) AHA_REQUIRE(cfg.integer("max_positions") <= e.max_positions, "config.json: max_positions exceeds the rows of 'pos'");
+        e.pos_table = e.vec(wt, "pos", (size_t)e.max_positions * e.W);
+    }
     int proj_cols = 1, inner_cols = 1, q_cols = 1;
     size_t route_ints = 0;
     for (int r = 0; r < e.L; ++r) {
@@ -1655,6 +1807,7 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
         rec.mixer = it->second(e, ly.at("mixer"), wt, p + "mix.", l);
         e.mixer_of_layer.push_back(rec.mixer.get());
         rec.pass = runs[r].second;
+        rec.reinject = e.parallel && rec.pass >= 1;
         auto conv_state = [&](const std::string& name, float*& w, float*& tails) {
             if (e.conv_taps < 1 || !wt.has(name)) return;
             w = e.vec(wt, name, (size_t)e.W * e.conv_taps);
@@ -1665,7 +1818,8 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
         if (e.sandwich) {
             rec.pre1 = e.vec(wt, p + "norm1", (size_t)e.W); rec.post1 = e.vec(wt, p + "norm1b", (size_t)e.W);
             conv_state(p + "canon1", rec.conv1, rec.tails1);
-        } else rec.gain1 = upload_scalar(e, wt, p + "norm1");
+        } else if (e.parallel) rec.pre1 = e.gain_vec(wt, p + "norm1", (size_t)e.W);
+        else rec.gain1 = upload_scalar(e, wt, p + "norm1");
         if (ly.has("mlp") && ly.at("mlp").kind == Json::Obj) {
             const Json& ml = ly.at("mlp");
             const std::string kind = ml.string_or("kind", "");
@@ -1675,7 +1829,7 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
             if (e.sandwich) {
                 rec.pre2 = e.vec(wt, p + "norm2", (size_t)e.W); rec.post2 = e.vec(wt, p + "norm2b", (size_t)e.W);
                 conv_state(p + "canon2", rec.conv2, rec.tails2);
-            } else rec.gain2 = upload_scalar(e, wt, p + "norm2");
+            } else if (!e.parallel) rec.gain2 = upload_scalar(e, wt, p + "norm2");
             route_ints = std::max(route_ints, rec.ff->route_ints());
         }
         for (Sublayer* s : {rec.mixer.get(), rec.ff.get()})
@@ -1692,6 +1846,12 @@ SeqEngine* make_layered_engine(Ctx& ctx, const Json& cfg, const WeightTable& wt,
     const size_t T = e.Tmax;
     e.x = ctx.alloc<float>(T * e.W); e.y = ctx.alloc<float>(T * e.W);
     if (e.sandwich) { e.hnorm = ctx.alloc<float>(T * e.W); e.hin = ctx.alloc<float>(T * e.W); }
+    if (e.parallel) {
+        e.hnorm = ctx.alloc<float>(T * e.W); e.y2 = ctx.alloc<float>(T * e.W);
+        bool again = false;
+        for (auto& ly : e.layers) again = again || ly.reinject;
+        if (again) e.x0 = ctx.alloc<float>(T * e.W);
+    }
     if (route_ints) e.route_buf = ctx.alloc<int>(route_ints);
     {
         size_t ga = 0, kvf = 0, of = 0, sh = 0;

@@ -74,7 +74,7 @@ class B200Model:
     def __init__(self, kind, config, weights, eos_ids=(), device=0, max_ctx=8192, max_prefill=0, max_patches=0,
                  max_frames=0, use_graph=True, decode_impl=0, gemm_impl=0, attn_impl=0, tp_rank=0, tp_world=1, tp_unique_id=None,
                  exact_fp32=False, max_seqs=0):
-        """kind "malasun" / "gatuzen" / "lupolorn": a layered-engine handle (config lists its layers); max_ctx = KV pool in tokens, max_prefill = tokens per
+        """kind "malasun" / "gatuzen" / "lupolorn" / "gomerax": a layered-engine handle (config lists its layers); max_ctx = KV pool in tokens, max_prefill = tokens per
         launch, max_seqs = state slots (0 = 8), exact_fp32 = every product in fp32 instead of bf16 weights."""
         self._lib = L.load()
         self.kind = kind
@@ -102,7 +102,7 @@ class B200Model:
         if rc != 0:
             raise B200Error(self._lib.aha_b200_last_error(None).decode())
         self._h = h
-        if kind in ("malasun", "gatuzen", "lupolorn", "layered"):
+        if kind in ("malasun", "gatuzen", "lupolorn", "gomerax", "layered"):
             self.vocab_size, self.hidden_size = config["vocab"], config["width"]
         else:
             tc = config if kind == "qwen3" else (config["text_config"] if kind == "qwen3vl" else config["thinker_config"]["text_config"])
