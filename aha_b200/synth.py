@@ -329,8 +329,104 @@ def make_malasun(cfg, seed=0, fast=False):
     return w
 
 
+
+def gomerax_config(layers, width=64, vocab=96, eps=1e-5, embed_scale=1.0, max_positions=512, loop=None):
+    """config.json of a Gomerax model.  layers: list of dicts
+         {"heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank", "window", "scale", "base"}
+       each with "ff": None | int (dense) | {"experts", "top", "ff", "limit", "scale", "groups": None | (count, keep), "shared": None | (ff, limit)}.
+       loop: None | (start, stop, times)."""
+    out = []
+    for ly in layers:
+        R = ly["rot_dim"]
+        mx = {"heads": ly["heads"], "dim": ly["dim"], "rot_dim": R, "vdim": ly["vdim"], "kv_rank": ly["kv_rank"], "q_rank": ly["q_rank"],
+              "mask": {"size": ly["window"]}, "rot": {"base": float(ly.get("base", 10000.0)), "dims": R},
+              "scale": float(ly.get("scale", (ly["dim"] + R) ** -0.5))}
+        ff = ly.get("ff")
+        if ff is None:
+            mlp = None
+        elif isinstance(ff, dict):
+            router = {"experts": ff["experts"], "top": ff["top"], "scale": float(ff.get("scale", 1.0))}
+            if ff.get("groups"):
+                router["groups"] = {"count": ff["groups"][0], "keep": ff["groups"][1]}
+            mlp = {"kind": "moe", "expert": {"ff": ff["ff"], "limit": float(ff.get("limit", 7.0))}, "router": router}
+            if ff.get("shared"):
+                mlp["shared"] = {"ff": ff["shared"][0], "limit": float(ff["shared"][1])}
+        else:
+            mlp = {"kind": "dense", "ff": int(ff)}
+        out.append({"type": "latent_attention", "mixer": mx, "mlp": mlp})
+    cfg = {"architecture": "Gomerax", "layers": out, "norm": {"eps": eps}, "embedding": {"scale": embed_scale}, "max_positions": max_positions,
+           "vocab": vocab, "width": width}
+    if loop:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def gomerax_shape(width, n_layers, heads, head_dim, ff, experts, top, expert_ff, vocab=32000, kv_rank=256, q_rank=512, rot_dim=32, window=1024, max_positions=4096,
+                  loop=None):
+    """A layer list of the sizes a served model would have: a dense feed-forward on the first layer, routed experts (groups of four, three kept) with a
+    shared expert on the others."""
+    layers = []
+    for i in range(n_layers):
+        f = ff if i == 0 else {"experts": experts, "top": top, "ff": expert_ff, "limit": 7.0, "scale": 2.5, "groups": (4, 3) if experts % 4 == 0 and experts >= 8 else None,
+                               "shared": (expert_ff, 7.0)}
+        layers.append({"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "kv_rank": kv_rank, "q_rank": q_rank, "window": window, "ff": f})
+    return gomerax_config(layers, width=width, vocab=vocab, eps=1e-6, embed_scale=float(np.sqrt(width)), max_positions=max_positions, loop=loop)
+
+
+def make_gomerax(cfg, seed=0, fast=False):
+    """Random weights under the checkpoint's tensor names, all bfloat16 (`_lib.BF16`-tagged bit patterns).  Norm gains are stored around zero."""
+    rng = np.random.default_rng(seed)
+    w = {}
+
+    def rnd(*shape, std=1.0):
+        if fast:
+            a = rng.random(int(np.prod(shape)), dtype=np.float32)
+            a -= np.float32(0.5)
+            a *= np.float32(std * 3.4641016)
+        else:
+            a = rng.standard_normal(int(np.prod(shape)), dtype=np.float32) * np.float32(std)
+        return a.reshape(shape)
+
+    def put(name, a):
+        w[name] = _bf16_round(a)
+
+    def lin(name, out_f, in_f, gain=1.0):
+        put(name, rnd(out_f, in_f, std=gain / np.sqrt(in_f)))
+
+    W, V = cfg["width"], cfg["vocab"]
+    put("embed", rnd(V, W, std=1.0 / max(1.0, cfg["embedding"]["scale"])))
+    put("pos", rnd(cfg["max_positions"], W, std=0.5))
+    put("final.norm", 0.2 * rnd(W))
+    for i, ly in enumerate(cfg["layers"]):
+        p, mx = "l%d." % i, ly["mixer"]
+        put(p + "norm1", 0.2 * rnd(W))
+        H, D, R, Dv, rank, qr = mx["heads"], mx["dim"], mx["rot_dim"], mx["vdim"], mx["kv_rank"], mx["q_rank"]
+        lin(p + "mix.dq", qr, W); put(p + "mix.dq.norm", 1.0 + 0.2 * rnd(qr)); lin(p + "mix.uq", H * (D + R), qr, 2.0)
+        lin(p + "mix.dkv", rank + R, W, 1.5); put(p + "mix.dkv.norm", 1.0 + 0.2 * rnd(rank))
+        lin(p + "mix.uk", H * D, rank, 2.0); lin(p + "mix.uv", H * Dv, rank); lin(p + "mix.o", W, H * Dv, 0.7)
+        put(p + "mix.sink", rnd(H, std=1.5))
+        ml = ly.get("mlp")
+        if not ml:
+            continue
+        if ml["kind"] == "dense":
+            ff = ml["ff"]
+            lin(p + "mlp.gate", ff, W, 1.5); lin(p + "mlp.up", ff, W); lin(p + "mlp.down", W, ff, 0.7)
+            put(p + "mlp.gate.b", rnd(ff, std=0.3)); put(p + "mlp.up.b", rnd(ff, std=0.3)); put(p + "mlp.down.b", rnd(W, std=0.1))
+        else:
+            ff, E = ml["expert"]["ff"], ml["router"]["experts"]
+            lim = ml["expert"]["limit"]
+            for e in range(E):      # (gains chosen so that the clamp cuts some of the values)
+                lin(p + "mlp.e%d.gate" % e, ff, W, 0.6 * lim); lin(p + "mlp.e%d.up" % e, ff, W, 0.6 * lim); lin(p + "mlp.e%d.down" % e, W, ff, 0.7 / max(1.0, lim))
+            lin(p + "mlp.router", E, W, 3.0)
+            put(p + "mlp.correction", rnd(E, std=0.1))
+            if ml.get("shared"):
+                fs, ls = ml["shared"]["ff"], ml["shared"]["limit"]
+                lin(p + "mlp.shared.gate", fs, W, 0.6 * ls); lin(p + "mlp.shared.up", fs, W, 0.6 * ls); lin(p + "mlp.shared.down", W, fs, 0.7 / max(1.0, ls))
+    return w
+
+
 def make_weights(kind, cfg, seed=0):
-    return {"qwen3": make_qwen3, "qwen3vl": make_qwen3vl, "qwen3_asr": make_qwen3_asr, "malasun": make_malasun, "gatuzen": make_gatuzen, "lupolorn": make_lupolorn}[kind](cfg, seed)
+    return {"qwen3": make_qwen3, "qwen3vl": make_qwen3vl, "qwen3_asr": make_qwen3_asr, "malasun": make_malasun, "gatuzen": make_gatuzen, "lupolorn": make_lupolorn, "gomerax": make_gomerax}[kind](cfg, seed)
 
 
 # ----------------------------------------------------------------------------- synthetic inputs
