@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "attention_window.cuh"
+#include "gemm_any.cuh"      // load_w8 / wt_to_f: weights as bf16 or fp32
 
 namespace aha {
 
@@ -53,6 +54,7 @@ struct LatentPrepArgs {
     RaggedBatch rb;
     // a query latent that is normed on the way (in place, gain per channel): columns ql_off .. ql_off + ql_rank - 1 of the projected rows; 0: none
     int ql_off = 0, ql_rank = 0; const float* ql_norm = nullptr;
+    int skip_q = 0;                 // 1: the queries' rotated parts are left alone (they do not exist yet: latent_absorb_kernel turns them later)
 };
 
 static __global__ void latent_prep_kernel(LatentPrepArgs a) {
@@ -79,7 +81,7 @@ static __global__ void latent_prep_kernel(LatentPrepArgs a) {
     // rotated parts: item (0, pair) is the shared key part, item (1 + h, pair) head h's query part; pairs beyond n_freq are single pass-through coordinates
     const int half = a.n_freq, rest = a.R - 2 * half, per = half + rest;
     const float fpos = (float)pos;
-    for (int idx = threadIdx.x; idx < (1 + a.H) * per; idx += blockDim.x) {
+    for (int idx = threadIdx.x; idx < (a.skip_q ? 1 : 1 + a.H) * per; idx += blockDim.x) {
         const int item = idx / per, j = idx % per;
         const float* src = item == 0 ? d + a.rank : row + a.q_off + (size_t)(item - 1) * (a.D + a.R) + a.D;
         float* dst = item == 0 ? krow + a.rank : a.q_abs + (size_t)t * a.ld_q + (size_t)(item - 1) * (a.rank + a.R) + a.rank;
@@ -475,21 +477,116 @@ static __global__ void __launch_bounds__(kLdThreads) latent_decode_attn_kernel(L
     }
 }
 
+// Decode-sized steps of a layer whose queries come through a latent and carry a rotated part: the absorbed query of every (token, head),
+//     q_abs[t][h] = [ W_uk(h)^T q_plain[t][h] | rot(q_rot[t][h], pos_t) ],
+// in ONE launch after the query expansion (the rotary embedding cannot run earlier, and a launch of its own would only move R numbers per
+// head).  A block owns (head, 64 rows of the head's transposed W_uk); thread r walks its row once, 16 bytes at a time, for all tokens of
+// the step (their unrotated query parts sit in shared memory), so the matrix is read once per step.  Block (h, 0) also turns the pairs.
+constexpr int kAbsorbMaxTokens = 8, kAbsorbThreads = 64;
+
+struct LatentAbsorbArgs {
+    const float* q; int ld; int q_off;     // [T, ld]: head h's query [D unrotated | R rotated] at column q_off + h * (D + R)
+    const void* uk_t;                      // [H * rank, D]: row h * rank + r is column r of the head's W_uk rows (bf16 or fp32)
+    float* q_abs; int ld_q;                // [T, H * (rank + R)]
+    const float* freq; int n_freq; float mult;
+    const int* tok_pos;
+    int T, H, D, R, rank;
+};
+
+template <typename WT>
+static __global__ void __launch_bounds__(kAbsorbThreads) latent_absorb_kernel(LatentAbsorbArgs a) {
+    extern __shared__ __align__(16) float ab_sm[];      // [T][D]
+    const int h = blockIdx.x, r = blockIdx.y * kAbsorbThreads + threadIdx.x;
+    for (int idx = threadIdx.x; idx < a.T * a.D; idx += kAbsorbThreads) {
+        const int t = idx / a.D, k = idx % a.D;
+        ab_sm[idx] = a.q[(size_t)t * a.ld + a.q_off + (size_t)h * (a.D + a.R) + k];
+    }
+    __syncthreads();
+    if (r < a.rank) {
+        const WT* w = reinterpret_cast<const WT*>(a.uk_t) + ((size_t)h * a.rank + r) * a.D;
+        float acc[kAbsorbMaxTokens];
+#pragma unroll
+        for (int t = 0; t < kAbsorbMaxTokens; ++t) acc[t] = 0.f;
+        if ((a.D & 7) == 0) {
+            for (int k0 = 0; k0 < a.D; k0 += 32) {      // four 16-byte pieces of the row requested before the first is used
+                float wv[4][8];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (k0 + 8 * u < a.D) load_w8(w + k0 + 8 * u, wv[u]);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int k = k0 + 8 * u;
+                    if (k < a.D) {
+#pragma unroll
+                        for (int t = 0; t < kAbsorbMaxTokens; ++t)
+                            if (t < a.T) {
+                                const float4 x0 = *reinterpret_cast<const float4*>(ab_sm + t * a.D + k), x1 = *reinterpret_cast<const float4*>(ab_sm + t * a.D + k + 4);
+                                acc[t] = fmaf(x1.w, wv[u][7], fmaf(x1.z, wv[u][6], fmaf(x1.y, wv[u][5], fmaf(x1.x, wv[u][4],
+                                         fmaf(x0.w, wv[u][3], fmaf(x0.z, wv[u][2], fmaf(x0.y, wv[u][1], fmaf(x0.x, wv[u][0], acc[t]))))))));
+                            }
+                    }
+                }
+            }
+        } else {
+            for (int k = 0; k < a.D; ++k) {
+                const float wk = wt_to_f(w[k]);
+#pragma unroll
+                for (int t = 0; t < kAbsorbMaxTokens; ++t)
+                    if (t < a.T) acc[t] = fmaf(ab_sm[t * a.D + k], wk, acc[t]);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < kAbsorbMaxTokens; ++t)
+            if (t < a.T) a.q_abs[(size_t)t * a.ld_q + (size_t)h * (a.rank + a.R) + r] = acc[t];
+    }
+    if (blockIdx.y == 0) {
+        const int half = a.n_freq, rest = a.R - 2 * half, per = half + rest;
+        for (int idx = threadIdx.x; idx < a.T * per; idx += kAbsorbThreads) {
+            const int t = idx / per, j = idx % per;
+            const float* src = a.q + (size_t)t * a.ld + a.q_off + (size_t)h * (a.D + a.R) + a.D;
+            float* dst = a.q_abs + (size_t)t * a.ld_q + (size_t)h * (a.rank + a.R) + a.rank;
+            if (j < half) {
+                float sn, cs;
+                sincosf((float)a.tok_pos[t] * a.freq[j], &sn, &cs);
+                sn *= a.mult; cs *= a.mult;
+                const float u = src[2 * j], v = src[2 * j + 1];
+                dst[2 * j] = u * cs - v * sn;
+                dst[2 * j + 1] = v * cs + u * sn;
+            } else {
+                const int c = 2 * half + (j - half);
+                dst[c] = src[c];
+            }
+        }
+    }
+}
+
+inline bool latent_absorb_supported(int T, int D) { return T <= kAbsorbMaxTokens && (size_t)T * D * sizeof(float) <= 48 * 1024; }
+inline void latent_absorb(cudaStream_t st, const LatentAbsorbArgs& a, bool fp32_weights) {
+    const dim3 grid(a.H, ceil_div(a.rank, kAbsorbThreads));
+    const size_t smem = (size_t)a.T * a.D * sizeof(float);
+    if (fp32_weights) latent_absorb_kernel<float><<<grid, kAbsorbThreads, smem, st>>>(a);
+    else latent_absorb_kernel<__nv_bfloat16><<<grid, kAbsorbThreads, smem, st>>>(a);
+    AHA_CUDA_CHECK(cudaGetLastError());
+}
+
 inline size_t latent_decode_smem(int Dk) { return ((size_t)kLdHG * Dk + kLdHG * kLdKeys + 3 * kLdHG) * sizeof(float); }
 inline bool latent_decode_supported(int Dk, int Dv) { return Dv <= 2 * kLdThreads && latent_decode_smem(Dk) <= 160 * 1024; }
 
 // kv_span: an upper bound of the keys any token of the step sees.  w: q, kv, scale, part, out, H, rb as for window_attn.  Returns the launches.
-inline int latent_decode_attn(cudaStream_t st, WindowAttnArgs w, int kv_span) {
+inline int latent_decode_attn(cudaStream_t st, WindowAttnArgs w, int kv_span, int num_sms = 148) {
     // the partial results of T tokens fit the workspace of window_attn (kWinSplitMaxTokens tokens x kWinMaxSplits chunks)
-    w.nsplit = std::max(1, std::min({kLdMaxSplits, ceil_div(kv_span, kLdKeys), kWinSplitMaxTokens * kWinMaxSplits / std::max(1, w.rb.T)}));
-    w.chunk = ceil_div(ceil_div(kv_span, w.nsplit), kPage) * kPage;
+    // a block walks tiles of kLdKeys keys; when full tiles would leave most SMs without a block (one or two decoded tokens, a short window) the
+    // chunks are half tiles, twice as many
+    const int keys = w.rb.T * ceil_div(kv_span, kLdKeys) >= num_sms ? kLdKeys : kLdKeys / 2;
+    w.nsplit = std::max(1, std::min({kLdMaxSplits, ceil_div(kv_span, keys), kWinSplitMaxTokens * kWinMaxSplits / std::max(1, w.rb.T)}));
+    w.chunk = ceil_div(ceil_div(kv_span, w.nsplit), keys) * keys;
     w.skip_from_n = 0;
     LatentDecodeArgs a{};
     a.q = w.q; a.ld_q = w.H * w.kv.D; a.kv = w.kv; a.scale = w.scale; a.part = w.part; a.nsplit = w.nsplit; a.chunk = w.chunk; a.H = w.H; a.window = w.window; a.rb = w.rb;
     static bool attr = false;
     if (!attr) { AHA_CUDA_CHECK(cudaFuncSetAttribute(latent_decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)); attr = true; }
     latent_decode_attn_kernel<<<dim3(w.rb.T, w.nsplit), kLdThreads, latent_decode_smem(w.kv.D), st>>>(a);
-    window_attn_merge_kernel<<<dim3(w.rb.T, w.H), kWinAttnThreads, 0, st>>>(w);
+    window_attn_merge_kernel<<<dim3(w.rb.T, w.H, ceil_div(w.kv.Dv, kWinAttnThreads)), kWinAttnThreads, 0, st>>>(w);
     AHA_CUDA_CHECK(cudaGetLastError());
     return 2;
 }

@@ -360,29 +360,19 @@ static __global__ void __launch_bounds__(kWinAttnThreads) window_attn_merge_kern
     const float L = block_sum(ls * wgt, red) + (a.sink ? expf(sk - M) : 0.f);
     if (mine) wsm[tid] = wgt / L;
     __syncthreads();
-    float o[kWinAttnMaxAcc];          // channels tid, tid + 128, ...: their loads of a chunk are in flight together
-#pragma unroll
-    for (int r = 0; r < kWinAttnMaxAcc; ++r) o[r] = 0.f;
-#pragma unroll 4
+    // a block sums ONE slice of 128 channels (blockIdx.z): a single decoded token still spreads over heads x slices blocks, and a thread's
+    // loads of several chunks are in flight together (a chunk without visible keys left no values: its weight is 0 and nothing is read)
+    const int c = tid + blockIdx.z * kWinAttnThreads;
+    if (c >= Dv) return;
+    float o = 0.f;
+#pragma unroll 8
     for (int s = 0; s < a.nsplit; ++s) {
         const float w = wsm[s];
-        if (w == 0.f) continue;           // a chunk without visible keys left no values
-        const float* ps = P + (size_t)s * (2 + Dv) + 2;
-#pragma unroll
-        for (int r = 0; r < kWinAttnMaxAcc; ++r) {
-            const int c = tid + r * kWinAttnThreads;
-            if (c < Dv) o[r] = fmaf(ps[c], w, o[r]);
-        }
+        const float v = w != 0.f ? P[(size_t)s * (2 + Dv) + 2 + c] : 0.f;
+        o = fmaf(v, w, o);
     }
-#pragma unroll
-    for (int r = 0; r < kWinAttnMaxAcc; ++r) {
-        const int c = tid + r * kWinAttnThreads;
-        if (c < Dv) {
-            float v = o[r];
-            if (a.gate) v *= sigmoid_f(a.gate[(size_t)t * a.gate_ld + (a.gate_per_head ? h : h * Dv + c)]);
-            a.out[(size_t)t * a.H * Dv + h * Dv + c] = v;
-        }
-    }
+    if (a.gate) o *= sigmoid_f(a.gate[(size_t)t * a.gate_ld + (a.gate_per_head ? h : h * Dv + c)]);
+    a.out[(size_t)t * a.H * Dv + h * Dv + c] = o;
 }
 
 // only_single: every entry of the step brings one token (the tails are moved along by the convolution kernel).  Returns the launches.
@@ -410,7 +400,7 @@ inline int window_attn(cudaStream_t st, WindowAttnArgs a, int kv_span) {
         a.chunk = ceil_div(ceil_div(kv_span, a.nsplit), kPage) * kPage;
         a.skip_from_n = 0;
         window_attn_kernel<true><<<dim3(a.rb.T, a.H, a.nsplit), kWinAttnThreads, smem, st>>>(a);
-        window_attn_merge_kernel<<<dim3(a.rb.T, a.H), kWinAttnThreads, 0, st>>>(a);
+        window_attn_merge_kernel<<<dim3(a.rb.T, a.H, ceil_div(a.kv.Dv, kWinAttnThreads)), kWinAttnThreads, 0, st>>>(a);
         AHA_CUDA_CHECK(cudaGetLastError());
         return 2;
     }

@@ -1284,7 +1284,9 @@ struct LatentAttentionMixer final : Sublayer {
         E.gemm(AEPI_STORE, v.x, E.W, in, E.proj, ld, T);
         // q = W_uq norm(W_dq h): the query latent is normed in place and the queries land behind the stacked projection.  Without a rotated part
         // the prep kernel has nothing to do on the queries themselves, so it runs first and norms the query latent on the way.
-        const bool norm_in_prep = q_rank > 0 && R == 0;
+        // Decode-sized steps with a rotated part as well: the prep kernel leaves the queries alone, and the launch that absorbs W_uk turns them.
+        const bool fused_absorb = q_rank > 0 && R > 0 && E.opt.seq_impl != 1 && latent_absorb_supported(T, D);
+        const bool norm_in_prep = q_rank > 0 && (R == 0 || fused_absorb);
         if (q_rank > 0 && !norm_in_prep) {
             E.tic("query latent norm", 4.0 * T * q_rank, 8.0 * T * q_rank);
             GroupNormArgs n{};
@@ -1298,6 +1300,7 @@ struct LatentAttentionMixer final : Sublayer {
         a.proj = E.proj; a.ld = ld; a.q_off = q_off; a.dkv_off = dkv_off; a.H = H; a.D = D; a.R = R; a.rank = rank; a.c_norm = c_norm; a.eps = E.eps;
         a.freq = freq; a.n_freq = n_freq; a.mult = rot_mult; a.q_abs = E.qbuf; a.ld_q = ldq; a.kv = kv; a.rb = v.rb;
         if (norm_in_prep) { a.ql_off = 0; a.ql_rank = q_rank; a.ql_norm = q_norm; }
+        a.skip_q = fused_absorb ? 1 : 0;
         latent_prep_kernel<<<T, T <= 8 ? 512 : 128, 0, st>>>(a);
         E.c.cnt.kernels++;
         AHA_CUDA_CHECK(cudaGetLastError());
@@ -1310,7 +1313,15 @@ struct LatentAttentionMixer final : Sublayer {
             any_long = any_long || lg; all_long = all_long && lg;
         }
         float* attn_out = E.lat_out;      // [T, H * Dv]
-        if (!all_long) {   // q_abs[t][h][:rank] = W_uk(h)^T q_plain[t][h]
+        if (fused_absorb) {      // (a decode-sized step has no long entries)
+            LatentAbsorbArgs b{};
+            b.q = E.proj; b.ld = ld; b.q_off = q_off; b.uk_t = uk_t.w; b.q_abs = E.qbuf; b.ld_q = ldq; b.freq = freq; b.n_freq = n_freq; b.mult = rot_mult;
+            b.tok_pos = v.rb.tok_pos; b.T = T; b.H = H; b.D = D; b.R = R; b.rank = rank;
+            E.tic("absorbed queries + rotary", 2.0 * T * H * rank * D, (double)H * rank * D * (E.fp32 ? 4 : 2) + 4.0 * T * H * (D + R + rank + R));
+            latent_absorb(st, b, E.fp32);
+            E.c.cnt.kernels++;
+            E.toc();
+        } else if (!all_long) {   // q_abs[t][h][:rank] = W_uk(h)^T q_plain[t][h]
             GemmAnyArgs g{};
             g.A = E.proj + q_off; g.lda = ld; g.W = uk_t.w; g.C = E.qbuf; g.ldc = ldq; g.M = T; g.N = rank; g.K = D;
             g.batch = H; g.a_bs = (size_t)(D + R); g.w_bs = (size_t)rank * D; g.c_bs = (size_t)(rank + R);
@@ -1324,7 +1335,7 @@ struct LatentAttentionMixer final : Sublayer {
             w.skip_from_n = any_long ? kLatentExpandMinTokens : 0;
             const int span = window > 0 ? std::min(window, v.span) : v.span;
             E.tic("latent attention (absorbed)", 2.0 * E.prof_pairs(window) * H * (2.0 * rank + R), 4.0 * (T * (double)H * (2.0 * rank + R) + E.prof_unique(window) * (rank + R)));
-            if (w.part && !any_long && T <= kWinSplitMaxTokens && latent_decode_supported(kv.D, kv.Dv)) E.c.cnt.kernels += latent_decode_attn(st, w, span);     // all heads share a block's key rows
+            if (w.part && !any_long && T <= kWinSplitMaxTokens && latent_decode_supported(kv.D, kv.Dv)) E.c.cnt.kernels += latent_decode_attn(st, w, span, E.c.num_sms);     // all heads share a block's key rows
             else E.c.cnt.kernels += window_attn(st, w, span);
             E.toc();
             // o[t][h] = W_uv(h) o_latent[t][h]  (rows of skipped entries are overwritten below)

@@ -562,6 +562,60 @@ def bench_lupolorn(args):
     emit(out)
 
 
+# ------------------------------------------------------------------------------------------------- --arch gomerax
+# width, layers (windowed latent attention with a rotated part and a sink everywhere; a dense feed-forward on the first layer, routed experts in groups + a
+# shared expert on the others; layers 1 and 2 run twice), heads / head size / rotated dims, dense ff, experts / top / expert ff, latent ranks, window
+GOMERAX_SIZES = {
+    "s": dict(width=1024, n_layers=6, heads=8, head_dim=128, rot_dim=64, ff=4096, experts=8, top=2, expert_ff=1024, kv_rank=256, q_rank=512, window=1024, vocab=32000, loop=(1, 3, 2)),
+    "m": dict(width=2048, n_layers=6, heads=16, head_dim=128, rot_dim=64, ff=8192, experts=16, top=2, expert_ff=2048, kv_rank=512, q_rank=1024, window=1024, vocab=32000, loop=(1, 3, 2)),
+    "l": dict(width=4096, n_layers=6, heads=32, head_dim=128, rot_dim=64, ff=12288, experts=32, top=4, expert_ff=2048, kv_rank=512, q_rank=1536, window=2048, vocab=32000, loop=(1, 3, 2)),
+}
+
+
+def bench_gomerax(args):
+    """Prefill (one 2048-token prompt portion) and decode (1 and 8 sequences at context 2048) of a Gomerax model with random weights, timed on
+    the device through the engine's own step, with the time of every kernel family against its roofline; beside it the engine's closest
+    design, Lupolorn, as a stack of as many windowed latent-attention layers as the Gomerax model has layer runs, with the same width, heads,
+    head size, latent ranks, window, experts and shared expert."""
+    from aha_b200 import B200Model, synth
+    hbm, hbm_src = measured_peaks()
+    try:
+        tf = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        tf = 1590.0
+    K, W = max(args.steps if args.steps != 128 else 16, 4), max(args.warmup, 3)
+    out = {"metric": "Gomerax prefill / decode tokens/s beside Lupolorn at equal size", "unit": UNIT, "data": "synthetic", "dtype": "bf16 weights, fp32 accumulate",
+           "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": hbm_src}, "prompt_tokens": 2048, "decode_ctx": 2048, "sizes": {}}
+    sampler = ClockSampler(0)
+    sampler.start()
+    for name in args.sizes.split(","):
+        sz = GOMERAX_SIZES[name]
+        cfg = synth.gomerax_shape(**sz)
+        log(f"[gomerax {name}] weights ...")
+        w = synth.make_gomerax(cfg, 0, fast=True)
+        m = B200Model("gomerax", cfg, w, max_ctx=8 * 4096, max_prefill=2048, max_seqs=8)
+        del w
+        rec = {"config": {k: (list(v) if isinstance(v, tuple) else v) for k, v in sz.items()}, "weight_bytes": m.stats()["weight_bytes"]}
+        rec.update(_profile_layered(m, "gomerax " + name, hbm, tf, W, K))
+        m.close()
+        runs = sz["n_layers"] + (sz["loop"][1] - sz["loop"][0]) * (sz["loop"][2] - 1)
+        moe = {"experts": sz["experts"], "top": sz["top"], "ff": sz["expert_ff"], "shared": sz["expert_ff"]}
+        lc = synth.lupolorn_config([{"type": "latent_attention", "heads": sz["heads"], "dim": sz["head_dim"], "vdim": sz["head_dim"], "kv_rank": sz["kv_rank"], "q_rank": sz["q_rank"],
+                                     "window": sz["window"], "ff": sz["ff"] if i == 0 else moe} for i in range(runs)],
+                                   width=sz["width"], vocab=sz["vocab"], eps=1e-6, embed_scale=float(sz["width"]) ** 0.5)
+        log(f"[lupolorn {name}] weights ...")
+        lw = synth.make_lupolorn(lc, 0, fast=True)
+        lm = B200Model("lupolorn", lc, lw, max_ctx=8 * 4096, max_prefill=2048, max_seqs=8)
+        del lw
+        lrec = {"weight_bytes": lm.stats()["weight_bytes"], "layers": runs}
+        lrec.update(_profile_layered(lm, "lupolorn " + name, hbm, tf, W, K))
+        lm.close()
+        rec["lupolorn_equal_size"] = lrec
+        out["sizes"][name] = rec
+    out["clocks"] = sampler.stop()
+    emit(out)
+
+
 def main():
     global _REAL_STDOUT
     sys.stdout.flush()
@@ -576,9 +630,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-tp", action="store_true", help="N > 1: skip the tensor-parallel (strong scaling) arm")
     ap.add_argument("--decode-impl", type=int, default=int(os.environ.get("AHA_DECODE_IMPL", "0")))
-    ap.add_argument("--arch", default="", help="'malasun' / 'gatuzen' / 'lupolorn': throughput of that design of the layered engine at model-like sizes beside its "
+    ap.add_argument("--arch", default="", help="'malasun' / 'gatuzen' / 'lupolorn' / 'gomerax': throughput of that design of the layered engine at model-like sizes beside its "
                                                "closest relative at equal size (a separate report; the default workload and its JSON line are unchanged)")
-    ap.add_argument("--sizes", default="s,m", help="--arch malasun / gatuzen / lupolorn: which of the sizes s, m, l to run")
+    ap.add_argument("--sizes", default="s,m", help="--arch malasun / gatuzen / lupolorn / gomerax: which of the sizes s, m, l to run")
     args = ap.parse_args()
     if args.arch == "malasun":
         return bench_malasun(args)
@@ -586,6 +640,8 @@ def main():
         return bench_gatuzen(args)
     if args.arch == "lupolorn":     # ... and for the Lupolorn design, beside Gatuzen at equal size
         return bench_lupolorn(args)
+    if args.arch == "gomerax":      # ... and for the Gomerax design, beside Lupolorn at equal size
+        return bench_gomerax(args)
     K, W = args.steps, max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
