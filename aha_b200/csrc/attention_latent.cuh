@@ -477,12 +477,11 @@ static __global__ void __launch_bounds__(kLdThreads) latent_decode_attn_kernel(L
     }
 }
 
-// Decode-sized steps of a layer whose queries come through a latent and carry a rotated part: the absorbed query of every (token, head),
+// Decode-sized steps: the absorbed query of every (token, head),
 //     q_abs[t][h] = [ W_uk(h)^T q_plain[t][h] | rot(q_rot[t][h], pos_t) ],
-// in ONE launch after the query expansion (the rotary embedding cannot run earlier, and a launch of its own would only move R numbers per
-// head).  A block owns (head, 64 rows of the head's transposed W_uk); thread r walks its row once, 16 bytes at a time, for all tokens of
-// the step (their unrotated query parts sit in shared memory), so the matrix is read once per step.  Block (h, 0) also turns the pairs.
-constexpr int kAbsorbMaxTokens = 8, kAbsorbThreads = 64;
+// in ONE launch (where the queries come through a latent of their own the rotary embedding cannot run before their expansion, and a launch
+// of its own would only move R numbers per head).
+constexpr int kAbsorbMaxTokens = 8, kAbsorbThreads = 128, kAbsorbRows = 64;
 
 struct LatentAbsorbArgs {
     const float* q; int ld; int q_off;     // [T, ld]: head h's query [D unrotated | R rotated] at column q_off + h * (D + R)
@@ -493,59 +492,78 @@ struct LatentAbsorbArgs {
     int T, H, D, R, rank;
 };
 
+// A block owns (head, 64 rows of the head's transposed W_uk).  Sixteen lanes share a row (a lane takes every sixteenth 16-byte piece of it: the
+// half warp reads 256 consecutive bytes), a warp walks two rows at a time and four such pairs with all their loads in flight; the unrotated
+// query parts of all tokens of the step sit in shared memory, so the matrix is read once per step.  Block (h, 0) also turns the pairs.
 template <typename WT>
 static __global__ void __launch_bounds__(kAbsorbThreads) latent_absorb_kernel(LatentAbsorbArgs a) {
     extern __shared__ __align__(16) float ab_sm[];      // [T][D]
-    const int h = blockIdx.x, r = blockIdx.y * kAbsorbThreads + threadIdx.x;
+    const int h = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane & 15, half = lane >> 4;
     for (int idx = threadIdx.x; idx < a.T * a.D; idx += kAbsorbThreads) {
         const int t = idx / a.D, k = idx % a.D;
         ab_sm[idx] = a.q[(size_t)t * a.ld + a.q_off + (size_t)h * (a.D + a.R) + k];
     }
     __syncthreads();
-    if (r < a.rank) {
-        const WT* w = reinterpret_cast<const WT*>(a.uk_t) + ((size_t)h * a.rank + r) * a.D;
-        float acc[kAbsorbMaxTokens];
+    const WT* W = reinterpret_cast<const WT*>(a.uk_t) + (size_t)h * a.rank * a.D;
+    const int r_base = blockIdx.y * kAbsorbRows + warp * (kAbsorbRows / 4) + half;      // this lane's rows: r_base + 2 i, i < 8
+    const bool vec = (a.D & 7) == 0;
+    for (int i0 = 0; i0 < kAbsorbRows / 8; i0 += 4) {
+        float acc[4][kAbsorbMaxTokens];
 #pragma unroll
-        for (int t = 0; t < kAbsorbMaxTokens; ++t) acc[t] = 0.f;
-        if ((a.D & 7) == 0) {
-            for (int k0 = 0; k0 < a.D; k0 += 32) {      // four 16-byte pieces of the row requested before the first is used
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int t = 0; t < kAbsorbMaxTokens; ++t) acc[u][t] = 0.f;
+        if (vec) {
+            for (int k = 8 * sub; k < a.D; k += 128) {
                 float wv[4][8];
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (k0 + 8 * u < a.D) load_w8(w + k0 + 8 * u, wv[u]);
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int k = k0 + 8 * u;
-                    if (k < a.D) {
-#pragma unroll
-                        for (int t = 0; t < kAbsorbMaxTokens; ++t)
-                            if (t < a.T) {
-                                const float4 x0 = *reinterpret_cast<const float4*>(ab_sm + t * a.D + k), x1 = *reinterpret_cast<const float4*>(ab_sm + t * a.D + k + 4);
-                                acc[t] = fmaf(x1.w, wv[u][7], fmaf(x1.z, wv[u][6], fmaf(x1.y, wv[u][5], fmaf(x1.x, wv[u][4],
-                                         fmaf(x0.w, wv[u][3], fmaf(x0.z, wv[u][2], fmaf(x0.y, wv[u][1], fmaf(x0.x, wv[u][0], acc[t]))))))));
-                            }
-                    }
-                }
-            }
-        } else {
-            for (int k = 0; k < a.D; ++k) {
-                const float wk = wt_to_f(w[k]);
+                for (int u = 0; u < 4; ++u) load_w8(W + (size_t)min(r_base + 2 * (i0 + u), a.rank - 1) * a.D + k, wv[u]);
 #pragma unroll
                 for (int t = 0; t < kAbsorbMaxTokens; ++t)
-                    if (t < a.T) acc[t] = fmaf(ab_sm[t * a.D + k], wk, acc[t]);
+                    if (t < a.T) {
+                        const float4 x0 = *reinterpret_cast<const float4*>(ab_sm + t * a.D + k), x1 = *reinterpret_cast<const float4*>(ab_sm + t * a.D + k + 4);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            acc[u][t] = fmaf(x1.w, wv[u][7], fmaf(x1.z, wv[u][6], fmaf(x1.y, wv[u][5], fmaf(x1.x, wv[u][4],
+                                        fmaf(x0.w, wv[u][3], fmaf(x0.z, wv[u][2], fmaf(x0.y, wv[u][1], fmaf(x0.x, wv[u][0], acc[u][t]))))))));
+                    }
+            }
+        } else {
+            for (int k = sub; k < a.D; k += 16) {
+                float wk[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) wk[u] = wt_to_f(W[(size_t)min(r_base + 2 * (i0 + u), a.rank - 1) * a.D + k]);
+#pragma unroll
+                for (int t = 0; t < kAbsorbMaxTokens; ++t)
+                    if (t < a.T) {
+                        const float x = ab_sm[t * a.D + k];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) acc[u][t] = fmaf(x, wk[u], acc[u][t]);
+                    }
             }
         }
 #pragma unroll
-        for (int t = 0; t < kAbsorbMaxTokens; ++t)
-            if (t < a.T) a.q_abs[(size_t)t * a.ld_q + (size_t)h * (a.rank + a.R) + r] = acc[t];
+        for (int u = 0; u < 4; ++u) {
+            const int r = r_base + 2 * (i0 + u);
+#pragma unroll
+            for (int t = 0; t < kAbsorbMaxTokens; ++t)
+                if (t < a.T) {      // (uniform over the warp)
+                    float v = acc[u][t];
+                    v += __shfl_xor_sync(0xffffffffu, v, 8);
+                    v += __shfl_xor_sync(0xffffffffu, v, 4);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    if (sub == 0 && r < a.rank) a.q_abs[(size_t)t * a.ld_q + (size_t)h * (a.rank + a.R) + r] = v;
+                }
+        }
     }
     if (blockIdx.y == 0) {
-        const int half = a.n_freq, rest = a.R - 2 * half, per = half + rest;
+        const int hf = a.n_freq, rest = a.R - 2 * hf, per = hf + rest;
         for (int idx = threadIdx.x; idx < a.T * per; idx += kAbsorbThreads) {
             const int t = idx / per, j = idx % per;
             const float* src = a.q + (size_t)t * a.ld + a.q_off + (size_t)h * (a.D + a.R) + a.D;
             float* dst = a.q_abs + (size_t)t * a.ld_q + (size_t)h * (a.rank + a.R) + a.rank;
-            if (j < half) {
+            if (j < hf) {
                 float sn, cs;
                 sincosf((float)a.tok_pos[t] * a.freq[j], &sn, &cs);
                 sn *= a.mult; cs *= a.mult;
@@ -553,7 +571,7 @@ static __global__ void __launch_bounds__(kAbsorbThreads) latent_absorb_kernel(La
                 dst[2 * j] = u * cs - v * sn;
                 dst[2 * j + 1] = v * cs + u * sn;
             } else {
-                const int c = 2 * half + (j - half);
+                const int c = 2 * hf + (j - hf);
                 dst[c] = src[c];
             }
         }
@@ -562,7 +580,7 @@ static __global__ void __launch_bounds__(kAbsorbThreads) latent_absorb_kernel(La
 
 inline bool latent_absorb_supported(int T, int D) { return T <= kAbsorbMaxTokens && (size_t)T * D * sizeof(float) <= 48 * 1024; }
 inline void latent_absorb(cudaStream_t st, const LatentAbsorbArgs& a, bool fp32_weights) {
-    const dim3 grid(a.H, ceil_div(a.rank, kAbsorbThreads));
+    const dim3 grid(a.H, ceil_div(a.rank, kAbsorbRows));
     const size_t smem = (size_t)a.T * a.D * sizeof(float);
     if (fp32_weights) latent_absorb_kernel<float><<<grid, kAbsorbThreads, smem, st>>>(a);
     else latent_absorb_kernel<__nv_bfloat16><<<grid, kAbsorbThreads, smem, st>>>(a);

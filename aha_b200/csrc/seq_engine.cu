@@ -1284,8 +1284,9 @@ struct LatentAttentionMixer final : Sublayer {
         E.gemm(AEPI_STORE, v.x, E.W, in, E.proj, ld, T);
         // q = W_uq norm(W_dq h): the query latent is normed in place and the queries land behind the stacked projection.  Without a rotated part
         // the prep kernel has nothing to do on the queries themselves, so it runs first and norms the query latent on the way.
-        // Decode-sized steps with a rotated part as well: the prep kernel leaves the queries alone, and the launch that absorbs W_uk turns them.
-        const bool fused_absorb = q_rank > 0 && R > 0 && E.opt.seq_impl != 1 && latent_absorb_supported(T, D);
+        // Decode-sized steps: the prep kernel leaves the queries alone, and ONE launch absorbs W_uk into them and turns their rotated parts.
+        // (One or two tokens of a layer that saves no launch by it stay on the batched product, which is a little faster there.)
+        const bool fused_absorb = E.opt.seq_impl != 1 && latent_absorb_supported(T, D) && (T >= 3 || (q_rank > 0 && R > 0));
         const bool norm_in_prep = q_rank > 0 && (R == 0 || fused_absorb);
         if (q_rank > 0 && !norm_in_prep) {
             E.tic("query latent norm", 4.0 * T * q_rank, 8.0 * T * q_rank);

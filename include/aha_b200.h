@@ -121,7 +121,7 @@ typedef struct aha_stats {
 
 /* XModel::new(cfg, VarBuilder, eos_ids) inside XGenerateModel::init
  * (/root/reference/src/models/qwen3/generate.rs:22-50, qwen3vl/generate.rs:33-63,
- *  qwen3_asr/generate.rs:51-87).  kind = "qwen3" | "qwen3vl" | "qwen3_asr" | "malasun" | "gatuzen" | "lupolorn" (layered engine, below); config_json is the
+ *  qwen3_asr/generate.rs:51-87).  kind = "qwen3" | "qwen3vl" | "qwen3_asr" | "malasun" | "gatuzen" | "lupolorn" | "gomerax" (layered engine, below); config_json is the
  * checkpoint's config.json text; weights are the safetensors tensors by name. */
 int aha_b200_create(const char* kind, const char* config_json,
                     const aha_tensor_desc* weights, size_t n_weights,
@@ -292,11 +292,13 @@ int aha_b200_rerank(aha_model* m, const uint32_t* query_ids, size_t query_len, c
                     size_t n_docs, float* scores_out);
 
 /* ---- layered sequence engine (new design; nothing like it in the reference) ----------------------------------------------------
- * kind = "malasun", "gatuzen" or "lupolorn" creates a handle for a model whose config.json LISTS its layers (config "layers": per layer a mixer
+ * kind = "malasun", "gatuzen", "lupolorn" or "gomerax" creates a handle for a model whose config.json LISTS its layers (config "layers": per layer a mixer
  * type -- gated linear recurrence "hgrn2" or windowed "attention" for Malasun; gated linear attention "gla", "mamba2" or "latent_attention" for
  * Gatuzen, whose layers also carry norms before and after every sublayer, an input convolution, table-routed experts and may be looped; the
  * elementwise recurrence "mingru", rotary "attention" with a sink in its softmax and windowed "latent_attention" for Lupolorn, with dense or
- * router-chosen experts -- with its sizes and constants, and an optional feed-forward).  Such a handle is served by one
+ * router-chosen experts; windowed "latent_attention" with a rotated part and a learned sink per head for Gomerax, whose layers run mixer and
+ * feed-forward side by side on one normed row, add learned position rows to the embedding and may be looped -- with its sizes and constants, and
+ * an optional feed-forward).  Such a handle is served by one
  * ragged step function: any mix of prompt portions and single tokens of different sequences in one step, over a paged KV pool
  * (aha_options.max_ctx tokens, 32-token pages from one free list) and aha_options.reserved[2] state slots (0 = 8; recurrent state,
  * convolution tails and sampler state of a sequence).  aha_options.reserved[1] = 1 selects exact fp32 arithmetic everywhere (weights widened
