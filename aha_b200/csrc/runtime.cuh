@@ -44,7 +44,7 @@ struct Ctx {  // per-handle launch context
 
     // Pre-split activations (two ping-pong buffers): a producer -- norm kernel, attention, GEMM epilogue -- writes the fp16 hi + lo
     // halves the next tensor-core GEMM reads, instead of an fp32 tensor that linear_gemm would have to read back and split.
-    bool presplit = true;         // AHA_PRESPLIT=0: every GEMM splits its own fp32 input (the round-1 data flow; results are bit-identical)
+    bool presplit = true;         // AHA_PRESPLIT=0: every GEMM splits its own fp32 input (the data flow without a shared split pass; results are bit-identical)
     __half* act_ws[2] = {nullptr, nullptr};
     size_t act_cap[2] = {0, 0};
     __half* act_split(int which, size_t halfs) {   // hi at the returned pointer, lo at + act_cap[which]

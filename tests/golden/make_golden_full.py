@@ -10,7 +10,7 @@ only what the GPU tests compare (tests/test_fullsize_gpu.py):
   * Qwen3-VL: f64 checksums (sum, sum |x|) of the four image-embed tensors (main + 3 deepstack) and a 64-row sample of each;
   * Qwen3-ASR: the same for the audio-tower output, and the oracle log-mel checksum.
 
-The oracle is the checker, never the product (oracle/__init__.py)."""
+The oracle is the yardstick, never the product (oracle/__init__.py)."""
 import os
 import sys
 import time
